@@ -9,9 +9,11 @@ Each schedule entry of a model may ask for one of two things:
   valid for every entry of its group, so one page table per group and sequence
   serves all its layers.  A windowed group gives pages back as soon as they fall
   wholly out of the window.
+  With ``values=False`` the group keeps one tensor only (``v`` is None): rows that
+  serve as keys and carry the values inside them, as latent attention's do.
 * ``StateRequest`` - a fixed-size tensor per sequence, ``[slots, *shape]``,
-  zeroed when a slot is taken.  The Llama decoder asks for none; the area
-  exists so that a recurrent mixer needs no change here.
+  zeroed when a slot is taken: the state of a recurrent mixer (retention's
+  ``[heads, dim, vdim]`` in float32).
 
 Lengths are per slot (all layers advance together inside a step).  Positions at
 or beyond a slot's length are never read, so a reused slot cannot see what its
@@ -35,6 +37,7 @@ class KVRequest:
     kv_heads: int
     head_dim: int
     window: int = 0
+    values: bool = True  # False: no storage for values (the key rows carry them)
 
 
 @dataclass(frozen=True)
@@ -58,7 +61,7 @@ class KVView:
     """What an attention-like part gets: its own layer of a group's storage."""
     group: int
     k: torch.Tensor  # [pages, kv_heads, page_size, head_dim]
-    v: torch.Tensor
+    v: Optional[torch.Tensor]  # None for a group without storage for values
     page_size: int
     window: int
     ahead: int = 0  # elements from k (and v) to those of the group's layer that runs next; 0: none
@@ -70,14 +73,14 @@ class StateView:
 
 
 class _KVGroup:
-    def __init__(self, key: Tuple[int, int, int], entries: List[int], pages: int,
+    def __init__(self, key: Tuple[int, int, int, bool], entries: List[int], pages: int,
                  dtype: torch.dtype, device: torch.device):
-        self.kv_heads, self.head_dim, self.window = key
+        self.kv_heads, self.head_dim, self.window, self.values = key
         self.entries = entries
         self.pool = FreeList(pages, "page")
         shape = (len(entries), pages, self.kv_heads, PAGE_SIZE, self.head_dim)
         self.k = torch.zeros(shape, dtype=dtype, device=device)
-        self.v = torch.zeros(shape, dtype=dtype, device=device)
+        self.v = torch.zeros(shape, dtype=dtype, device=device) if self.values else None
         # per slot: logical page index -> page id, -1 where given back
         self.tables: Dict[int, List[int]] = {}
 
@@ -109,10 +112,10 @@ class CacheManager:
         self.owners: List[int] = [0] * max_slots  # how many sequences have held each slot
         self.groups: List[_KVGroup] = []
         self._views: List[Optional[Union[KVView, StateView]]] = []
-        by_key: Dict[Tuple[int, int, int], List[int]] = {}
+        by_key: Dict[Tuple[int, int, int, bool], List[int]] = {}
         for i, r in enumerate(requests):
             if isinstance(r, KVRequest):
-                by_key.setdefault((r.kv_heads, r.head_dim, r.window), []).append(i)
+                by_key.setdefault((r.kv_heads, r.head_dim, r.window, bool(r.values)), []).append(i)
         group_of: Dict[int, Tuple[int, int]] = {}
         for key, entries in by_key.items():
             g = _KVGroup(key, entries, self.pages_total, dtype, self.device)
@@ -125,7 +128,7 @@ class CacheManager:
                 gi, j = group_of[i]
                 g = self.groups[gi]
                 nxt = (j + 1) % len(g.entries)  # (after the last layer: the first, in the next step)
-                self._views.append(KVView(gi, g.k[j], g.v[j], PAGE_SIZE, g.window,
+                self._views.append(KVView(gi, g.k[j], g.v[j] if g.values else None, PAGE_SIZE, g.window,
                                           (nxt - j) * g.k[0].numel()))
             elif isinstance(r, StateRequest):
                 t = torch.zeros((max_slots, *r.shape), dtype=r.dtype, device=self.device)
@@ -279,7 +282,7 @@ class CacheManager:
     def kv_bytes_per_token(self) -> int:
         """Bytes of keys and values that one position of one sequence holds over all
         layers (a windowed group counted like a full one)."""
-        return sum(2 * len(g.entries) * g.kv_heads * g.head_dim * g.k.element_size()
+        return sum((2 if g.values else 1) * len(g.entries) * g.kv_heads * g.head_dim * g.k.element_size()
                    for g in self.groups)
 
     # -- telemetry (crates/nnis-rt/src/kv_telemetry.rs:42-80) ----------------
@@ -289,7 +292,7 @@ class CacheManager:
             "pages_held": [g.pool.held for g in self.groups], "pages_total": self.pages_total,
             "live_tokens": sum(self.lengths[s] for s in range(self.slots.count)
                                if self.slots.is_held(s)),
-            "kv_bytes": sum(g.k.numel() * g.k.element_size() * 2 for g in self.groups),
+            "kv_bytes": sum(g.k.numel() * g.k.element_size() * (2 if g.values else 1) for g in self.groups),
         }
 
     def check(self) -> None:

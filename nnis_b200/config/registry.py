@@ -15,6 +15,7 @@ import os
 from typing import Any, Dict, Mapping, Type
 
 from .llama import ConfigError, LlamaConfig
+from .nafezen import NafezenConfig
 from .spec import ModelSpec
 
 _ARCHITECTURES: Dict[str, Type] = {}
@@ -32,6 +33,15 @@ def known_architectures():
 
 
 def config_from_dict(raw: Mapping[str, Any]):
+    # a configuration names its architecture either as Hugging Face does (a list of one
+    # name under "architectures") or by a plain "architecture" string
+    if "architectures" not in raw and isinstance(raw.get("architecture"), str):
+        name = raw["architecture"]
+        cls = _ARCHITECTURES.get(name)
+        if cls is None:
+            raise ConfigError(f"config.json: unknown architecture {name!r}; "
+                              f"known: {known_architectures()}")
+        return cls.from_dict(raw)
     archs = raw.get("architectures")
     if not isinstance(archs, list) or len(archs) != 1 or not isinstance(archs[0], str):
         raise ConfigError(f"config.json: architectures must be a list of one name; got {archs!r}")
@@ -70,3 +80,4 @@ def spec_from_dir(model_dir: str) -> ModelSpec:
 
 
 register_architecture(LlamaConfig.architecture, LlamaConfig)
+register_architecture(NafezenConfig.architecture, NafezenConfig)

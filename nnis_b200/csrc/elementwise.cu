@@ -184,6 +184,83 @@ __global__ void rope_store_kernel(T* __restrict__ qkv, const int* __restrict__ t
     }
 }
 
+
+// ---------------------------------------------------------------------------
+// RMS norm in groups: a row of `width` is cut into `groups` equal runs, each
+// divided by its own sqrt(mean(run^2) + eps), and the whole multiplied by w.
+// A warp per (row, group); a lane reads the same elements in both passes, so
+// y may be x itself (float32 output).
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(256)
+group_rmsnorm_kernel(const float* x, const int* __restrict__ rows,
+                     const float* __restrict__ w, T* y, long long n_units, int width, int groups,
+                     float eps) {
+    long long unit = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (unit >= n_units) return;
+    int lane = threadIdx.x & 31;
+    long long r = unit / groups;
+    int g = (int)(unit - r * groups), gw = width / groups;
+    const float* in = x + (size_t)(rows ? rows[r] : r) * width + (size_t)g * gw;
+    float ss = 0.f;
+    for (int i = lane; i < gw; i += 32) ss = fmaf(in[i], in[i], ss);
+    ss = warp_sum(ss);
+    float s = 1.0f / sqrtf(ss / (float)gw + eps);
+    T* out = y + (size_t)r * width + (size_t)g * gw;
+    const float* wg = w + (size_t)g * gw;
+    for (int i = lane; i < gw; i += 32) out[i] = from_float<T>((in[i] * s) * wg[i]);
+}
+
+// ---------------------------------------------------------------------------
+// out[n, i] = relu(u[n, i])^2 (* sigmoid(u[n, inter]) when `gated`): the
+// activation of an expert whose row of u carries, as its last column, the logit
+// of a gate that scales the expert's whole output.  u float32 [n, inter + gated].
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void relu2_gate_kernel(const float* __restrict__ u, T* __restrict__ out, size_t n_rows,
+                                  int inter, int gated) {
+    size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= n_rows * (size_t)inter) return;
+    size_t n = idx / inter;
+    int i = (int)(idx - n * inter);
+    const float* row = u + n * (size_t)(inter + gated);
+    float a = fmaxf(row[i], 0.f);
+    float v = a * a;
+    if (gated) v *= 1.0f / (1.0f + expf(-row[inter]));
+    out[idx] = from_float<T>(v);
+}
+
+// ---------------------------------------------------------------------------
+// Rotation of a part of every head by frequencies given as a table: for each
+// token n and head h, the `len` elements at src[n, h * src_head + src_off ...]
+// go to dst[n, h * dst_head + dst_off ...]; the first `dims` of them are turned
+// in pairs (i, i + dims / 2) by the angle pos * freq[i] (float32), the rest pass.
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void rope_part_kernel(const T* __restrict__ src, long long src_row, int src_head,
+                                 int src_off, T* __restrict__ dst, long long dst_row, int dst_head,
+                                 int dst_off, const int* __restrict__ token_pos,
+                                 const float* __restrict__ freq, int heads, int len, int dims) {
+    int n = blockIdx.x;
+    int pos = token_pos[n];
+    int half = dims >> 1;
+    int items = heads * (len - half);  // a pair, or one element beyond the turned ones
+    for (int it = threadIdx.x; it < items; it += blockDim.x) {
+        int h = it / (len - half), j = it - h * (len - half);
+        const T* s = src + (size_t)n * src_row + (size_t)h * src_head + src_off;
+        T* d = dst + (size_t)n * dst_row + (size_t)h * dst_head + dst_off;
+        if (j < half) {
+            float a = to_float(s[j]), b = to_float(s[j + half]);
+            float ang = (float)(pos < 0 ? 0 : pos) * freq[j];
+            float c = cosf(ang), sn = sinf(ang);
+            d[j] = from_float<T>(a * c - b * sn);
+            d[j + half] = from_float<T>(b * c + a * sn);
+        } else {
+            d[j + half] = s[j + half];
+        }
+    }
+}
+
 }  // namespace nnis
 
 using namespace nnis;
@@ -278,6 +355,59 @@ NNIS_API int nnis_rope_store(void* qkv, int dtype, const int* token_pos, const i
         rope_store_kernel<bf16><<<n_tokens, threads, 0, stream>>>(
             (bf16*)qkv, token_pos, token_seq, page_table, table_cols, cos_t, sin_t, (bf16*)k_cache,
             (bf16*)v_cache, nq, nkv, d, page_size, rotate);
+    else
+        return NNIS_ERR_UNSUPPORTED;
+    NNIS_RETURN_LAUNCH();
+}
+
+NNIS_API int nnis_group_rmsnorm(const float* x, const int* rows, const float* w, void* y,
+                                int out_dtype, int n_rows, int width, int groups, float eps,
+                                cudaStream_t stream) {
+    if (n_rows <= 0 || width <= 0 || groups <= 0 || width % groups || !(eps > 0.f))
+        return NNIS_ERR_ARGUMENT;
+    long long units = (long long)n_rows * groups;
+    unsigned blocks = (unsigned)((units + 7) / 8);
+    if (out_dtype == NNIS_DTYPE_F32)
+        group_rmsnorm_kernel<float><<<blocks, 256, 0, stream>>>(x, rows, w, (float*)y, units, width,
+                                                                groups, eps);
+    else if (out_dtype == NNIS_DTYPE_BF16)
+        group_rmsnorm_kernel<bf16><<<blocks, 256, 0, stream>>>(x, rows, w, (bf16*)y, units, width,
+                                                               groups, eps);
+    else
+        return NNIS_ERR_UNSUPPORTED;
+    NNIS_RETURN_LAUNCH();
+}
+
+NNIS_API int nnis_relu2_gate(const float* u, void* out, int out_dtype, long long n_rows, int inter,
+                             int gated, cudaStream_t stream) {
+    if (n_rows <= 0 || inter <= 0 || (gated != 0 && gated != 1)) return NNIS_ERR_ARGUMENT;
+    size_t total = (size_t)n_rows * inter;
+    unsigned blocks = (unsigned)((total + 255) / 256);
+    if (out_dtype == NNIS_DTYPE_F32)
+        relu2_gate_kernel<float><<<blocks, 256, 0, stream>>>(u, (float*)out, n_rows, inter, gated);
+    else if (out_dtype == NNIS_DTYPE_BF16)
+        relu2_gate_kernel<bf16><<<blocks, 256, 0, stream>>>(u, (bf16*)out, n_rows, inter, gated);
+    else
+        return NNIS_ERR_UNSUPPORTED;
+    NNIS_RETURN_LAUNCH();
+}
+
+NNIS_API int nnis_rope_part(const void* src, long long src_row, int src_head, int src_off, void* dst,
+                            long long dst_row, int dst_head, int dst_off, const int* token_pos,
+                            const float* freq, int n_tokens, int heads, int len, int dims, int dtype,
+                            cudaStream_t stream) {
+    if (n_tokens <= 0 || heads <= 0 || len <= 0 || dims < 0 || (dims & 1) || dims > len || !freq)
+        return NNIS_ERR_ARGUMENT;
+    int work = heads * (len - dims / 2);
+    int threads = work >= 256 ? 256 : (work >= 128 ? 128 : 64);
+    if (dtype == NNIS_DTYPE_F32)
+        rope_part_kernel<float><<<n_tokens, threads, 0, stream>>>(
+            (const float*)src, src_row, src_head, src_off, (float*)dst, dst_row, dst_head, dst_off,
+            token_pos, freq, heads, len, dims);
+    else if (dtype == NNIS_DTYPE_BF16)
+        rope_part_kernel<bf16><<<n_tokens, threads, 0, stream>>>(
+            (const bf16*)src, src_row, src_head, src_off, (bf16*)dst, dst_row, dst_head, dst_off,
+            token_pos, freq, heads, len, dims);
     else
         return NNIS_ERR_UNSUPPORTED;
     NNIS_RETURN_LAUNCH();

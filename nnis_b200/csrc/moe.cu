@@ -1,0 +1,175 @@
+// Mixture of experts, token by token: a router picks `top` of `experts` small
+// feed-forward layers W_down act(W_up h), act = relu^2, and the token's output is
+// the sum of theirs weighted by a softmax over the chosen logits only.
+//
+//   moe_route   logits z = W_r h + b in float32 (a warp per token), the `top` largest
+//               (ties to the lower index), softmax over those -> ids, weights
+//   moe_up      act[n, s, :] = relu(W_up[id[n, s]] h_n)^2: a warp per output feature
+//   moe_down    residual[n, :] += sum_s weight[n, s] W_down[id[n, s]] act[n, s, :], the
+//               chosen experts added in the router's order (the same bits every time)
+//
+// Expert weights are stacked: W_up [experts, ff, width], W_down [experts, width, ff].
+// A row whose position is -1 (padding) is skipped everywhere.
+#include <float.h>
+
+#include "common.cuh"
+
+namespace nnis {
+
+template <typename T>
+__global__ void __launch_bounds__(128)
+moe_route_kernel(const T* __restrict__ h, const float* __restrict__ wr, const float* __restrict__ br,
+                 const int* __restrict__ token_pos, int* __restrict__ ids,
+                 float* __restrict__ weights, int n_tokens, int width, int experts, int top) {
+    extern __shared__ float z_smem[];
+    int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    int n = blockIdx.x * 4 + warp;
+    if (n >= n_tokens) return;
+    int* id = ids + (size_t)n * top;
+    float* wt = weights + (size_t)n * top;
+    if (token_pos[n] < 0) {
+        for (int s = lane; s < top; s += 32) {
+            id[s] = 0;
+            wt[s] = 0.f;
+        }
+        return;
+    }
+    float* z = z_smem + (size_t)warp * experts;
+    const T* x = h + (size_t)n * width;
+    for (int e = 0; e < experts; ++e) {
+        const float* w = wr + (size_t)e * width;
+        float acc = 0.f;
+        for (int i = lane; i < width; i += 32) acc = fmaf(w[i], to_float(x[i]), acc);
+        acc = warp_sum(acc);
+        if (lane == 0) z[e] = acc + (br ? br[e] : 0.f);
+    }
+    __syncwarp();
+    // the `top` largest, one after another; lanes share the search
+    float first = 0.f, total = 0.f;
+    for (int s = 0; s < top; ++s) {
+        float best = -FLT_MAX;
+        int arg = 0x7fffffff;
+        for (int e = lane; e < experts; e += 32) {
+            float v = z[e];
+            if (v > best) {  // (ascending e: the lower index wins a tie)
+                best = v;
+                arg = e;
+            }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            int oa = __shfl_xor_sync(0xffffffffu, arg, o);
+            if (ob > best || (ob == best && oa < arg)) {
+                best = ob;
+                arg = oa;
+            }
+        }
+        if (s == 0) first = best;
+        float p = expf(best - first);
+        total += p;
+        if (lane == 0) {
+            id[s] = arg;
+            wt[s] = p;
+            z[arg] = -FLT_MAX;
+        }
+        __syncwarp();
+    }
+    float inv = 1.0f / total;
+    __syncwarp();
+    for (int s = lane; s < top; s += 32) wt[s] *= inv;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+moe_up_kernel(const T* __restrict__ h, const T* __restrict__ w_up, const int* __restrict__ ids,
+              const int* __restrict__ token_pos, T* __restrict__ act, int width, int ff, int top) {
+    int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    long long pair = blockIdx.x;
+    int f = blockIdx.y * 8 + warp;
+    long long n = pair / top;
+    if (f >= ff || token_pos[n] < 0) return;
+    const T* w = w_up + ((size_t)ids[pair] * ff + f) * width;
+    const T* x = h + (size_t)n * width;
+    float acc = 0.f;
+    for (int i = lane; i < width; i += 32) acc = fmaf(to_float(w[i]), to_float(x[i]), acc);
+    acc = warp_sum(acc);
+    if (lane == 0) {
+        float a = fmaxf(acc, 0.f);
+        act[(size_t)pair * ff + f] = from_float<T>(a * a);
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+moe_down_kernel(const T* __restrict__ act, const T* __restrict__ w_down, const int* __restrict__ ids,
+                const float* __restrict__ weights, const int* __restrict__ token_pos,
+                float* __restrict__ residual, int width, int ff, int top) {
+    int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    long long n = blockIdx.x;
+    int c = blockIdx.y * 8 + warp;
+    if (c >= width || token_pos[n] < 0) return;
+    float sum = 0.f;
+    for (int s = 0; s < top; ++s) {
+        const T* w = w_down + ((size_t)ids[n * top + s] * width + c) * ff;
+        const T* a = act + ((size_t)n * top + s) * ff;
+        float acc = 0.f;
+        for (int i = lane; i < ff; i += 32) acc = fmaf(to_float(w[i]), to_float(a[i]), acc);
+        acc = warp_sum(acc);
+        sum = fmaf(weights[n * top + s], acc, sum);
+    }
+    if (lane == 0) residual[(size_t)n * width + c] += sum;
+}
+
+}  // namespace nnis
+
+using namespace nnis;
+
+NNIS_API int nnis_moe_route(const void* h, const float* wr, const float* br, const int* token_pos,
+                            int* ids, float* weights, int n_tokens, int width, int experts, int top,
+                            int dtype, cudaStream_t stream) {
+    if (n_tokens <= 0 || width <= 0 || experts <= 0 || top <= 0 || top > experts || !h || !wr || !ids ||
+        !weights || !token_pos)
+        return NNIS_ERR_ARGUMENT;
+    size_t smem = 4 * (size_t)experts * sizeof(float);
+    if (smem > 48 * 1024) return NNIS_ERR_UNSUPPORTED;
+    unsigned blocks = (unsigned)((n_tokens + 3) / 4);
+    if (dtype == NNIS_DTYPE_F32)
+        moe_route_kernel<float><<<blocks, 128, smem, stream>>>((const float*)h, wr, br, token_pos, ids,
+                                                               weights, n_tokens, width, experts, top);
+    else if (dtype == NNIS_DTYPE_BF16)
+        moe_route_kernel<bf16><<<blocks, 128, smem, stream>>>((const bf16*)h, wr, br, token_pos, ids,
+                                                              weights, n_tokens, width, experts, top);
+    else
+        return NNIS_ERR_UNSUPPORTED;
+    NNIS_RETURN_LAUNCH();
+}
+
+// act: operand dtype [n_tokens, top, ff] (scratch); residual: float32 [n_tokens, width]
+NNIS_API int nnis_moe_experts(const void* h, const void* w_up, const void* w_down, const int* ids,
+                              const float* weights, const int* token_pos, void* act, float* residual,
+                              int n_tokens, int width, int ff, int top, int dtype,
+                              cudaStream_t stream) {
+    if (n_tokens <= 0 || width <= 0 || ff <= 0 || top <= 0 || !h || !w_up || !w_down || !ids ||
+        !weights || !token_pos || !act || !residual)
+        return NNIS_ERR_ARGUMENT;
+    if ((ff + 7) / 8 > 65535 || (width + 7) / 8 > 65535) return NNIS_ERR_UNSUPPORTED;
+    dim3 up_grid((unsigned)((long long)n_tokens * top), (ff + 7) / 8);
+    dim3 down_grid(n_tokens, (width + 7) / 8);
+    if (dtype == NNIS_DTYPE_F32) {
+        moe_up_kernel<float><<<up_grid, 256, 0, stream>>>((const float*)h, (const float*)w_up, ids,
+                                                          token_pos, (float*)act, width, ff, top);
+        moe_down_kernel<float><<<down_grid, 256, 0, stream>>>((const float*)act, (const float*)w_down,
+                                                              ids, weights, token_pos, residual, width,
+                                                              ff, top);
+    } else if (dtype == NNIS_DTYPE_BF16) {
+        moe_up_kernel<bf16><<<up_grid, 256, 0, stream>>>((const bf16*)h, (const bf16*)w_up, ids,
+                                                         token_pos, (bf16*)act, width, ff, top);
+        moe_down_kernel<bf16><<<down_grid, 256, 0, stream>>>((const bf16*)act, (const bf16*)w_down, ids,
+                                                             weights, token_pos, residual, width, ff,
+                                                             top);
+    } else {
+        return NNIS_ERR_UNSUPPORTED;
+    }
+    NNIS_RETURN_LAUNCH();
+}

@@ -924,3 +924,175 @@ def trace_end():
     names = [lib.nnis_trace_name(i).decode() for i in range(int(lib.nnis_trace_count()))]
     lib.nnis_trace_set(None, 0)
     return names
+
+
+# ---------------------------------------------------------------------------
+# norm in groups, per-head products, latent attention, retention, experts
+# ---------------------------------------------------------------------------
+def group_rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, groups: int, out: torch.Tensor,
+                  rows: Optional[torch.Tensor] = None) -> None:
+    """out[r] = x[rows[r]] (or x[r]) with each of ``groups`` equal runs divided by its own
+    root mean square, times weight; statistics in float32.  ``out`` may be ``x`` itself."""
+    _cuda(x, weight, out, rows)
+    n, width = out.shape
+    _need(x.dtype == torch.float32 and x.shape[1] == width, "x: float32 [*, width]")
+    _need(weight.dtype == torch.float32 and weight.numel() == width, "weight: float32 [width]")
+    _need(groups > 0 and width % groups == 0, f"norm: {groups} groups do not divide the width {width}")
+    if rows is not None:
+        _need(rows.dtype == torch.int32 and rows.numel() >= n, "rows: int32 [n]")
+    else:
+        _need(x.shape[0] >= n, "x has fewer rows than out")
+    _check(_lib().nnis_group_rmsnorm(_ptr(x), _ptr(rows), _ptr(weight), _ptr(out), code_of(out.dtype), n,
+                                     width, groups, ctypes.c_float(eps), _stream()), "group_rmsnorm")
+
+
+def relu2_gate(u: torch.Tensor, out: torch.Tensor, gated: bool) -> None:
+    """out = relu(u[:, :I])^2, times sigmoid(u[:, I]) when ``gated``; u float32 [n, I + gated]."""
+    _cuda(u, out)
+    n, inter = out.shape
+    _need(u.dtype == torch.float32 and tuple(u.shape) == (n, inter + int(gated)),
+          "u: float32 [n, inter + gated]")
+    _check(_lib().nnis_relu2_gate(_ptr(u), _ptr(out), code_of(out.dtype), ctypes.c_longlong(n), inter,
+                                  int(gated), _stream()), "relu2_gate")
+
+
+def rope_part(src: torch.Tensor, src_head: int, src_off: int, dst: torch.Tensor, dst_head: int,
+              dst_off: int, token_pos: torch.Tensor, freq: torch.Tensor, heads: int, length: int,
+              dims: int) -> None:
+    """For every row n and head h, the ``length`` elements at src[n, h * src_head + src_off]
+    go to dst[n, h * dst_head + dst_off]; the first ``dims`` are turned in pairs (i, i +
+    dims / 2) by the angle position * freq[i], the rest pass unchanged."""
+    _cuda(src, dst, token_pos, freq)
+    n = src.shape[0]
+    _need(src.dtype == dst.dtype and dst.shape[0] == n, "rope_part: src and dst of one dtype and row count")
+    _need(src_off + length <= src_head and (heads - 1) * src_head + src_off + length <= src.shape[1],
+          "rope_part: the part lies outside src's heads")
+    _need(dst_off + length <= dst_head and (heads - 1) * dst_head + dst_off + length <= dst.shape[1],
+          "rope_part: the part lies outside dst's heads")
+    _need(freq.dtype == torch.float32 and freq.numel() >= dims // 2 and dims % 2 == 0 and dims <= length,
+          "rope_part: freq float32 [dims / 2]")
+    _need(token_pos.dtype == torch.int32 and token_pos.numel() >= n, "rope_part: token_pos int32 [n]")
+    _check(_lib().nnis_rope_part(_ptr(src), ctypes.c_longlong(src.shape[1]), src_head, src_off, _ptr(dst),
+                                 ctypes.c_longlong(dst.shape[1]), dst_head, dst_off, _ptr(token_pos),
+                                 _ptr(freq), n, heads, length, dims, code_of(src.dtype), _stream()),
+           "rope_part")
+
+
+def batched_linear(a: torch.Tensor, a_head: int, w: torch.Tensor, out: torch.Tensor, out_head: int) -> None:
+    """out[m, b * out_head : + N] = a[m, b * a_head : + K] . w[b]^T for every head b;
+    w [heads, N, K]; a and out packed rows whose heads are ``a_head`` / ``out_head`` apart."""
+    _cuda(a, w, out)
+    heads, n, k = w.shape
+    m = a.shape[0]
+    _need(a.dtype == w.dtype == out.dtype and out.shape[0] == m, "batched_linear: one dtype, equal rows")
+    _need(k <= a_head and (heads - 1) * a_head + k <= a.shape[1], "batched_linear: K lies outside a's heads")
+    _need(n <= out_head and (heads - 1) * out_head + n <= out.shape[1],
+          "batched_linear: N lies outside out's heads")
+    _check(_lib().nnis_batched_linear(_ptr(a), ctypes.c_longlong(a.shape[1]), ctypes.c_longlong(a_head),
+                                      _ptr(w), _ptr(out), ctypes.c_longlong(out.shape[1]),
+                                      ctypes.c_longlong(out_head), heads, m, n, k, code_of(a.dtype),
+                                      _stream()), "batched_linear")
+
+
+def latent_prep(a: torch.Tensor, wq: torch.Tensor, wkv: torch.Tensor, freq: torch.Tensor,
+                token_pos: torch.Tensor, token_seq: torch.Tensor, page_table: torch.Tensor,
+                cq: torch.Tensor, cache: torch.Tensor, q_rank: int, kv_rank: int, rot: int,
+                rot_dims: int, eps: float) -> None:
+    """From the down-projection's float32 rows [q latent | c raw | kr raw]: the normed q
+    latent to ``cq``; the normed c and the rotated kr into the cache row of each token."""
+    _cuda(a, wq, wkv, freq, token_pos, token_seq, page_table, cq, cache)
+    n = a.shape[0]
+    _need(a.dtype == torch.float32 and a.shape[1] == q_rank + kv_rank + rot, "latent_prep: a float32 rows")
+    _need(wq.dtype == wkv.dtype == freq.dtype == torch.float32 and wq.numel() == q_rank
+          and wkv.numel() == kv_rank and freq.numel() >= rot_dims // 2, "latent_prep: float32 vectors")
+    _need(cq.dtype == cache.dtype and tuple(cq.shape) == (n, q_rank), "latent_prep: cq [n, q_rank]")
+    _need(cache.dim() == 4 and cache.shape[1] == 1 and cache.shape[3] == kv_rank + rot,
+          "latent_prep: cache [pages, 1, page, kv_rank + rot]")
+    _need(page_table.dtype == torch.int32 and token_pos.dtype == torch.int32, "latent_prep: int32 tables")
+    _check(_lib().nnis_latent_prep(_ptr(a), _ptr(wq), _ptr(wkv), _ptr(freq), _ptr(token_pos),
+                                   _ptr(token_seq), _ptr(page_table), page_table.shape[1], _ptr(cq),
+                                   _ptr(cache), n, q_rank, kv_rank, rot, rot_dims, cache.shape[2],
+                                   ctypes.c_float(eps), code_of(cq.dtype), _stream()), "latent_prep")
+
+
+def attention_latent(q: torch.Tensor, cache: torch.Tensor, token_pos: torch.Tensor,
+                     token_seq: torch.Tensor, page_table: torch.Tensor, out: torch.Tensor, heads: int,
+                     dv: int, scale: float, n_splits: int = 1,
+                     partial: Optional[torch.Tensor] = None) -> None:
+    """Causal attention of packed queries [n, heads * dk] over cache rows [pages, 1, page,
+    dk] shared by all heads; the rows' first ``dv`` values are the values.  out [n, heads * dv]."""
+    _cuda(q, cache, token_pos, token_seq, page_table, out, partial)
+    n = out.shape[0]
+    pages, one, page_size, dk = cache.shape
+    _need(one == 1 and q.shape[1] == heads * dk and out.shape[1] == heads * dv and 0 < dv <= dk,
+          "attention_latent: q [n, heads * dk], out [n, heads * dv]")
+    _need(q.dtype == cache.dtype == out.dtype, "attention_latent: one dtype")
+    _need(pages * page_size < 2 ** 31, "attention_latent: the cache has too many rows")
+    if n_splits > 1:
+        _need(partial is not None and partial.dtype == torch.float32
+              and partial.numel() >= n * heads * n_splits * (dv + 2), "attention_latent: partial scratch")
+    _check(_lib().nnis_attention_latent(_ptr(q), _ptr(cache), _ptr(token_pos), _ptr(token_seq),
+                                        _ptr(page_table), page_table.shape[1], _ptr(out), _ptr(partial), n,
+                                        heads, dk, dv, page_size, ctypes.c_float(scale), n_splits,
+                                        code_of(out.dtype), _stream()),
+           "attention_latent", 2 if n_splits > 1 else 1)
+
+
+def retention(qkvg: torch.Tensor, freq: torch.Tensor, decay: torch.Tensor, state: torch.Tensor,
+              token_pos: torch.Tensor, token_seq: torch.Tensor, seq_slots: torch.Tensor,
+              seq_first_row: Optional[torch.Tensor], seq_start: Optional[torch.Tensor],
+              seq_count: Optional[torch.Tensor], o_raw: torch.Tensor, out: torch.Tensor, heads: int,
+              dim: int, vdim: int, rot_dims: int, eps: float) -> None:
+    """Retention of packed rows [q | k | v | g] from and into the per-slot state
+    [slots, heads, dim, vdim] (float32); out [n, heads * vdim] = o / rms(o) * silu(g).
+    Without ``seq_first_row`` every row is one token of a sequence of its own."""
+    _cuda(qkvg, freq, decay, state, token_pos, token_seq, seq_slots, seq_first_row, seq_start, seq_count,
+          o_raw, out)
+    n = out.shape[0]
+    _need(qkvg.shape[0] >= n and qkvg.shape[1] == 2 * heads * (dim + vdim) and qkvg.dtype == out.dtype,
+          "retention: rows [n, 2 heads (dim + vdim)]")
+    _need(state.dtype == torch.float32 and tuple(state.shape[1:]) == (heads, dim, vdim),
+          "retention: state float32 [slots, heads, dim, vdim]")
+    _need(decay.dtype == torch.float32 and decay.numel() == heads and freq.dtype == torch.float32
+          and freq.numel() >= rot_dims // 2, "retention: decay [heads], freq [rot_dims / 2] float32")
+    _need(o_raw.dtype == torch.float32 and o_raw.numel() >= n * heads * vdim, "retention: scratch")
+    _need(out.shape[1] == heads * vdim, "retention: out [n, heads * vdim]")
+    units = seq_first_row.numel() if seq_first_row is not None else n
+    _check(_lib().nnis_retention(_ptr(qkvg), _ptr(freq), _ptr(decay), _ptr(state), _ptr(token_pos),
+                                 _ptr(token_seq), _ptr(seq_slots), _ptr(seq_first_row), _ptr(seq_start),
+                                 _ptr(seq_count), _ptr(o_raw), _ptr(out), n, units, heads, dim, vdim,
+                                 rot_dims, ctypes.c_float(eps), code_of(out.dtype), _stream()),
+           "retention", 2)
+
+
+def moe_route(h: torch.Tensor, w_router: torch.Tensor, b_router: Optional[torch.Tensor],
+              token_pos: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, top: int) -> None:
+    """ids, weights [n, top]: the ``top`` experts with the largest float32 logits
+    w_router . h + b_router and the softmax over their logits."""
+    _cuda(h, w_router, b_router, token_pos, ids, weights)
+    n, width = h.shape
+    experts = w_router.shape[0]
+    _need(w_router.dtype == torch.float32 and w_router.shape[1] == width, "moe_route: router float32 [E, width]")
+    _need(b_router is None or (b_router.dtype == torch.float32 and b_router.numel() == experts),
+          "moe_route: bias float32 [E]")
+    _need(ids.dtype == torch.int32 and weights.dtype == torch.float32 and ids.numel() >= n * top
+          and weights.numel() >= n * top and 0 < top <= experts, "moe_route: ids int32, weights float32 [n, top]")
+    _check(_lib().nnis_moe_route(_ptr(h), _ptr(w_router), _ptr(b_router), _ptr(token_pos), _ptr(ids),
+                                 _ptr(weights), n, width, experts, top, code_of(h.dtype), _stream()),
+           "moe_route")
+
+
+def moe_experts(h: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor, ids: torch.Tensor,
+                weights: torch.Tensor, token_pos: torch.Tensor, act: torch.Tensor,
+                residual: torch.Tensor, top: int) -> None:
+    """residual[n] += sum over the chosen experts of weight * W_down[e] relu(W_up[e] h[n])^2."""
+    _cuda(h, w_up, w_down, ids, weights, token_pos, act, residual)
+    n, width = h.shape
+    experts, ff, _ = w_up.shape
+    _need(tuple(w_up.shape) == (experts, ff, width) and tuple(w_down.shape) == (experts, width, ff)
+          and h.dtype == w_up.dtype == w_down.dtype == act.dtype, "moe_experts: stacked weights of one dtype")
+    _need(act.numel() >= n * top * ff, "moe_experts: act scratch [n, top, ff]")
+    _need(residual.dtype == torch.float32 and tuple(residual.shape) == (n, width), "moe_experts: residual")
+    _check(_lib().nnis_moe_experts(_ptr(h), _ptr(w_up), _ptr(w_down), _ptr(ids), _ptr(weights),
+                                   _ptr(token_pos), _ptr(act), _ptr(residual), n, width, ff, top,
+                                   code_of(h.dtype), _stream()), "moe_experts", 2)

@@ -1,4 +1,5 @@
-from . import attention, block, embedding, mlp, norm, position  # noqa: F401  (registration)
+from . import (attention, block, embedding, latent_attention, mlp, moe, norm, position,  # noqa: F401
+               retention)  # (registration)
 from .base import (BLOCKS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS, POSITIONS, Part,
                    PositionEncoding, Registry)
 from .block import Block

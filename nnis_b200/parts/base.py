@@ -31,7 +31,7 @@ float32 in every dtype, and a fused epilogue may add in place.
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import Any, Callable, Dict, Mapping
+from typing import Any, Callable, Dict, Mapping, Optional
 
 import torch
 
@@ -82,9 +82,14 @@ class Part:
         self.prefix = prefix
         self.dtype = dtype
         self.device = device
+        # what a matrix's or a norm's tensor name ends in ("weight" as Hugging Face
+        # checkpoints have it; "" where the stem is the whole name)
+        self.leaf = params.get("leaf", "weight") if hasattr(params, "get") else "weight"
 
-    def tensor_name(self, stem: str, leaf: str = "weight") -> str:
-        return f"{self.prefix}.{stem}.{leaf}" if self.prefix else f"{stem}.{leaf}"
+    def tensor_name(self, stem: str, leaf: Optional[str] = None) -> str:
+        leaf = self.leaf if leaf is None else leaf
+        name = f"{stem}.{leaf}" if leaf else stem
+        return f"{self.prefix}.{name}" if self.prefix else name
 
     def weight_specs(self) -> Dict[str, WeightSpec]:
         return {}

@@ -6,6 +6,8 @@ its parts from ``LayerSpec.parts`` by the roles it knows, so one with other or m
 sub-layers (a post-norm, one norm for parallel branches, a third sub-layer) is a
 class registered in ``BLOCKS``, not a change here.
 
+``parallel``: with n = norm(h), h += mixer(n) + ffn(n); roles norm, mixer, ffn.
+
 ``prenorm``: h += mixer(norm1(h)); h += ffn(norm2(h)) - the order of NNIS's
 decoder (crates/nnis-model/src/runtime.rs:946-1097); roles mixer_norm, mixer,
 ffn_norm, ffn.  In decode steps a norm may be shared out between the projections on
@@ -123,4 +125,31 @@ class PreNormBlock(Block):
         ctx.emit_for = None
 
 
+class ParallelBlock(Block):
+    """One norm, two branches that both read it: with h = norm(x),
+    x += mixer(h) + ffn(h).  Roles: norm, mixer and, optionally, ffn (a layer
+    without a feed-forward has none).  Both branches add into the float32 residual;
+    the feed-forward reads the normed rows, which the mixer leaves as they are."""
+
+    def __init__(self, layer_spec, dtype: torch.dtype, device: torch.device):
+        super().__init__(layer_spec, dtype, device)
+        self.norm = self.build(NORMS, "norm")
+        self.mixer = self.build(MIXERS, "mixer")
+        self.ffn = self.build(FEED_FORWARDS, "ffn") if "ffn" in layer_spec.parts else None
+
+    def parts(self):
+        return tuple(p for p in (self.norm, self.mixer, self.ffn) if p is not None)
+
+    def forward(self, hidden: torch.Tensor, ctx, cache) -> None:
+        n, width = hidden.shape
+        # (a buffer of its own: parts may use "normed" for their own rows)
+        normed = ctx.workspace.get("normed_parallel", (n, width), self.dtype)
+        ctx.emit_for = None  # the next norm reads both branches' sum: no part may begin it
+        self.norm.forward(hidden, normed)
+        self.mixer.forward(normed, ctx, hidden, cache)
+        if self.ffn is not None:
+            self.ffn.forward(normed, ctx, hidden)
+
+
 BLOCKS.register("prenorm", PreNormBlock)
+BLOCKS.register("parallel", ParallelBlock)

@@ -12,7 +12,7 @@ import torch
 
 from ..csrc import ops
 from ..weights.loader import WeightSpec
-from .base import EMBEDDINGS, HEADS, Part
+from .base import EMBEDDINGS, HEADS, NORMS, Part
 from .linear import STORE_F32, linear
 
 
@@ -34,6 +34,27 @@ class TokenEmbedding(Part):
 
     def forward(self, tokens: torch.Tensor, hidden: torch.Tensor, status: torch.Tensor) -> None:
         ops.embed(self.table, tokens, hidden, status)
+
+
+class NormedTokenEmbedding(TokenEmbedding):
+    """The same followed by a norm of the embedded rows (in place, float32).
+    params: vocab_size, hidden_size, name, norm (a PartSpec of ``NORMS``)."""
+
+    def __init__(self, params, prefix, dtype, device):
+        super().__init__(params, prefix, dtype, device)
+        norm = params["norm"]
+        self.norm = NORMS.build(norm.kind, norm.params, prefix, dtype, device)
+
+    def weight_specs(self) -> Dict[str, WeightSpec]:
+        return {**super().weight_specs(), **self.norm.weight_specs()}
+
+    def load(self, tensors: Mapping[str, torch.Tensor]) -> None:
+        super().load(tensors)
+        self.norm.load(tensors)
+
+    def forward(self, tokens: torch.Tensor, hidden: torch.Tensor, status: torch.Tensor) -> None:
+        ops.embed(self.table, tokens, hidden, status)
+        self.norm.forward(hidden, hidden)
 
 
 class LinearHead(Part):
@@ -90,4 +111,5 @@ class LinearHead(Part):
 
 
 EMBEDDINGS.register("token_embedding", TokenEmbedding)
+EMBEDDINGS.register("normed_token_embedding", NormedTokenEmbedding)
 HEADS.register("linear_head", LinearHead)

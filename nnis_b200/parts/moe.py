@@ -1,0 +1,103 @@
+"""Mixture of experts: every token runs ``top`` of ``experts`` small feed-forward
+layers and, optionally, a shared one.
+
+An expert is ``W_down act(W_up h)`` with act = relu squared, no biases.  The router's
+logits ``z = W_r h + b`` are float32 (its matrix is kept in float32); the ``top``
+largest choose the experts and a softmax over the chosen logits alone weighs them.
+The shared expert has the same form, runs for every token and is multiplied by
+``sigmoid(w_sg . h)``, one number per token; that number is an extra output row of
+the shared expert's up-projection, and since it scales the whole output it is
+applied to the activation, before the down-projection adds into the residual.
+
+The experts' matrices are stacked ([experts, ff, width] and [experts, width, ff]) so
+that one kernel serves all of them from the router's ids.
+
+params: hidden_size, experts, top, ff, shared_ff (0: no shared expert), activation
+("relu2"), names {router, router_bias, expert (a format with {e}), up, down,
+shared_up, shared_down, shared_gate}.
+"""
+from __future__ import annotations
+
+from typing import Dict, Mapping
+
+import torch
+
+from ..csrc import ops
+from ..weights.loader import WeightSpec
+from .base import FEED_FORWARDS, Part
+from .linear import ADD_F32, STORE_F32, linear
+
+
+class MoEFeedForward(Part):
+    def __init__(self, params, prefix, dtype, device):
+        super().__init__(params, prefix, dtype, device)
+        self.hidden = int(params["hidden_size"])
+        self.experts = int(params["experts"])
+        self.top = int(params["top"])
+        self.ff = int(params["ff"])
+        self.shared_ff = int(params.get("shared_ff") or 0)
+        self.names = params["names"]
+        if params.get("activation", "relu2") != "relu2":
+            raise ValueError(f"moe: activation {params['activation']!r} has no kernel")
+        if not 0 < self.top <= self.experts:
+            raise ValueError(f"moe: top={self.top} of {self.experts} experts")
+        self.w_router = self.b_router = self.w_up = self.w_down = None
+        self.w_shared_up = self.w_shared_down = None
+
+    def _expert(self, e: int, which: str) -> str:
+        return self.tensor_name(self.names["expert"].format(e=e) + "." + self.names[which])
+
+    def weight_specs(self) -> Dict[str, WeightSpec]:
+        W = self.hidden
+        # the router is held in float32 whatever the operand dtype ("vector": kept as float32)
+        specs = {self.tensor_name(self.names["router"]): WeightSpec((self.experts, W), "vector", fan_in=W),
+                 self.tensor_name(self.names["router_bias"]): WeightSpec((self.experts,), "vector")}
+        for e in range(self.experts):
+            specs[self._expert(e, "up")] = WeightSpec((self.ff, W), "matrix", fan_in=W)
+            specs[self._expert(e, "down")] = WeightSpec((W, self.ff), "matrix", fan_in=self.ff)
+        if self.shared_ff:
+            specs[self.tensor_name(self.names["shared_up"])] = WeightSpec((self.shared_ff, W), "matrix", fan_in=W)
+            specs[self.tensor_name(self.names["shared_down"])] = WeightSpec((W, self.shared_ff), "matrix",
+                                                                           fan_in=self.shared_ff)
+            specs[self.tensor_name(self.names["shared_gate"])] = WeightSpec((1, W), "matrix", fan_in=W)
+        return specs
+
+    def load(self, tensors: Mapping[str, torch.Tensor]) -> None:
+        self.w_router = tensors[self.tensor_name(self.names["router"])]
+        self.b_router = tensors[self.tensor_name(self.names["router_bias"])]
+        self.w_up = torch.stack([tensors[self._expert(e, "up")] for e in range(self.experts)]).contiguous()
+        self.w_down = torch.stack([tensors[self._expert(e, "down")] for e in range(self.experts)]).contiguous()
+        if self.shared_ff:
+            self.w_shared_up = torch.cat([tensors[self.tensor_name(self.names["shared_up"])],
+                                          tensors[self.tensor_name(self.names["shared_gate"])]], 0).contiguous()
+            self.w_shared_down = tensors[self.tensor_name(self.names["shared_down"])]
+
+    def parameter_bytes(self) -> int:
+        """What a step of one token reads: the router, ``top`` experts, the shared one."""
+        per_expert = 2 * self.ff * self.hidden * self.w_up.element_size()
+        shared = sum(t.numel() * t.element_size() for t in (self.w_shared_up, self.w_shared_down)
+                     if t is not None)
+        return self.w_router.numel() * 4 + self.top * per_expert + shared
+
+    def step_flops(self, counts, starts) -> float:
+        W = self.hidden
+        per_token = W * self.experts + 2 * self.top * self.ff * W + self.shared_ff * (2 * W + 1) + W
+        return 2.0 * sum(counts) * per_token
+
+    def forward(self, x: torch.Tensor, ctx, residual: torch.Tensor) -> None:
+        n = residual.shape[0]
+        ws = ctx.workspace
+        ids = ws.get("moe_ids", (n, self.top), torch.int32)
+        weights = ws.get("moe_weights", (n, self.top), torch.float32)
+        ops.moe_route(x, self.w_router, self.b_router, ctx.token_pos, ids, weights, self.top)
+        act = ws.get("moe_act", (n, self.top, self.ff), self.dtype)
+        ops.moe_experts(x, self.w_up, self.w_down, ids, weights, ctx.token_pos, act, residual, self.top)
+        if self.shared_ff:
+            up = ws.get("moe_shared_up", (n, self.shared_ff + 1), torch.float32)
+            linear(x, self.w_shared_up, None, up, STORE_F32)
+            shared_act = ws.get("moe_shared_act", (n, self.shared_ff), self.dtype)
+            ops.relu2_gate(up, shared_act, True)
+            linear(shared_act, self.w_shared_down, None, residual, ADD_F32, ws)
+
+
+FEED_FORWARDS.register("moe", MoEFeedForward)

@@ -35,4 +35,23 @@ class RMSNorm(Part):
         ops.rmsnorm(x, self.weight, self.eps, out, rows)
 
 
+class GroupRMSNorm(RMSNorm):
+    """RMS norm in groups: the row is cut into ``groups`` equal consecutive runs, each
+    divided by its own sqrt(mean(run^2) + eps), and the whole multiplied by the weight.
+    params: size, eps, groups, name.  No projection folds this norm into itself (its
+    ``kind`` is not "rmsnorm"), so it always runs as a kernel of its own."""
+    kind = "group_rmsnorm"
+
+    def __init__(self, params, prefix, dtype, device):
+        super().__init__(params, prefix, dtype, device)
+        self.groups = int(params.get("groups", 1))
+        if self.groups <= 0 or self.size % self.groups:
+            raise ValueError(f"norm: {self.groups} groups do not divide {self.size}")
+
+    def forward(self, x: torch.Tensor, out: torch.Tensor,
+                rows: Optional[torch.Tensor] = None) -> None:
+        ops.group_rmsnorm(x, self.weight, self.eps, self.groups, out, rows)
+
+
 NORMS.register("rmsnorm", RMSNorm)
+NORMS.register("group_rmsnorm", GroupRMSNorm)

@@ -39,10 +39,36 @@ class RotaryHalf(PositionEncoding):
         return _TABLES[self.key]
 
 
+class RotaryFrequencies(PositionEncoding):
+    """Rotate-half rotation of the first ``dims`` of a vector by angles position *
+    base^(-2i/dims), i = 0 .. dims/2 - 1, with the angle and its cosine and sine
+    computed in float32 inside the kernels from a table of the ``dims / 2`` frequencies:
+    no table of positions, so no bound on them.  params: dims, base.  Mixers whose
+    kernels take frequencies (latent attention, retention) ask for ``frequencies()``."""
+
+    def __init__(self, params, prefix, dtype, device):
+        super().__init__(params, prefix, dtype, device)
+        self.dims = int(params["dims"])
+        self.base = float(params["base"])
+        if self.dims < 0 or self.dims % 2:
+            raise ValueError(f"rotation: dims={self.dims} must be even")
+        self._freq: Optional[torch.Tensor] = None
+
+    def frequencies(self) -> torch.Tensor:
+        if self._freq is None:
+            half = self.dims // 2
+            exponent = -(2 * torch.arange(half, dtype=torch.float32)) / float(max(self.dims, 1))
+            freq = torch.pow(torch.tensor(self.base, dtype=torch.float32), exponent)
+            # (one spare entry so that dims == 0 still has an address)
+            self._freq = torch.cat([freq, torch.zeros(1)]).to(self.device).contiguous()
+        return self._freq
+
+
 class NoPosition(PositionEncoding):
     def rotary_tables(self):
         return None
 
 
 POSITIONS.register("rope_half", RotaryHalf)
+POSITIONS.register("rope_frequencies", RotaryFrequencies)
 POSITIONS.register("none", NoPosition)

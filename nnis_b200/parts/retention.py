@@ -1,0 +1,96 @@
+"""Retention: linear attention with a fixed decay per head and a state of fixed size.
+
+Per head, with q = W_q h and k = W_k h rotated by position (rotate-half over the
+first ``rot dims``) and k scaled by dim^-1/2, v = W_v h:
+
+    S_t = decay_h * S_{t-1} + k_t v_t^T        o_t = S_t^T q_t
+
+No softmax, no denominator.  Each head's o is divided by its root mean square (no
+weight), the heads are joined, multiplied by silu(W_g h) and projected by W_o into
+the residual stream.  S [heads, dim, vdim] is float32, starts at zero and is the
+layer's whole memory of a sequence: it lives in the cache's state area, one per
+slot, so a later chunk or a single token goes on from what the tokens before left.
+
+params: hidden_size, heads, dim, vdim, decay (one per head), eps, position (a
+``rope_frequencies`` PartSpec), names {q, k, v, g, o}.
+"""
+from __future__ import annotations
+
+from typing import Dict, Mapping
+
+import torch
+
+from ..cache import StateRequest, StateView
+from ..csrc import ops
+from ..weights.loader import WeightSpec
+from .base import MIXERS, POSITIONS, Part
+from .linear import ADD_F32, STORE, linear
+
+
+class Retention(Part):
+    def __init__(self, params, prefix, dtype, device):
+        super().__init__(params, prefix, dtype, device)
+        self.hidden = int(params["hidden_size"])
+        self.heads = int(params["heads"])
+        self.dim = int(params["dim"])
+        self.vdim = int(params["vdim"])
+        self.eps = float(params["eps"])
+        self.decay_values = [float(d) for d in params["decay"]]
+        self.names = params["names"]
+        if len(self.decay_values) != self.heads:
+            raise ValueError(f"retention: {len(self.decay_values)} decays for {self.heads} heads")
+        if not 0 < self.dim <= 256:
+            raise ValueError("retention kernels take key sizes up to 256")
+        pos = params["position"]
+        self.position = POSITIONS.build(pos.kind, pos.params, prefix, dtype, device)
+        if not hasattr(self.position, "frequencies"):
+            raise ValueError("retention rotates by a table of frequencies (rope_frequencies)")
+        if self.position.dims > self.dim:
+            raise ValueError(f"rotation over {self.position.dims} dimensions of heads of {self.dim}")
+        self.w_in = self.w_o = None
+        self._decay = None
+
+    def _name(self, key: str) -> str:
+        return self.tensor_name(self.names[key])
+
+    def weight_specs(self) -> Dict[str, WeightSpec]:
+        W, H = self.hidden, self.heads
+        return {self._name("q"): WeightSpec((H * self.dim, W), "matrix", fan_in=W),
+                self._name("k"): WeightSpec((H * self.dim, W), "matrix", fan_in=W),
+                self._name("v"): WeightSpec((H * self.vdim, W), "matrix", fan_in=W),
+                self._name("g"): WeightSpec((H * self.vdim, W), "matrix", fan_in=W),
+                self._name("o"): WeightSpec((W, H * self.vdim), "matrix", fan_in=H * self.vdim)}
+
+    def load(self, tensors: Mapping[str, torch.Tensor]) -> None:
+        self.w_in = torch.cat([tensors[self._name(p)] for p in ("q", "k", "v", "g")], 0).contiguous()
+        self.w_o = tensors[self._name("o")]
+        self._decay = torch.tensor(self.decay_values, dtype=torch.float32, device=self.w_o.device)
+
+    def parameter_bytes(self) -> int:
+        return sum(t.numel() * t.element_size() for t in (self.w_in, self.w_o))
+
+    def cache_request(self) -> StateRequest:
+        return StateRequest((self.heads, self.dim, self.vdim), torch.float32)
+
+    def check_shared_cache(self, view) -> None:
+        raise ValueError("retention keeps a state of its own")
+
+    def step_flops(self, counts, starts) -> float:
+        H, W = self.heads, self.hidden
+        return 2.0 * sum(counts) * (W * 2 * H * (self.dim + self.vdim) + H * self.vdim * W
+                                    + 2 * H * self.dim * self.vdim)
+
+    def forward(self, x: torch.Tensor, ctx, residual: torch.Tensor, cache: StateView) -> None:
+        n = residual.shape[0]
+        H, ws = self.heads, ctx.workspace
+        qkvg = ws.get("retention_in", (n, 2 * H * (self.dim + self.vdim)), self.dtype)
+        linear(x, self.w_in, None, qkvg, STORE)
+        o_raw = ws.get("retention_o", (n, H * self.vdim), torch.float32)
+        gated = ws.get("retention_gated", (n, H * self.vdim), self.dtype)
+        ops.retention(qkvg, self.position.frequencies(), self._decay, cache.state, ctx.token_pos,
+                      ctx.token_seq, ctx.seq_slots, ctx.seq_first_row, ctx.seq_start, ctx.seq_count,
+                      o_raw, gated, H, self.dim, self.vdim, self.position.dims, self.eps)
+        linear(gated, self.w_o, None, residual, ADD_F32, ws)
+
+
+MIXERS.register("retention", Retention)
