@@ -63,7 +63,9 @@ def rotate(x: Tensor, base: float, dims: int) -> Tensor:
     return torch.cat([u * c - v * s, v * c + u * s, x[..., dims:].to(F)], dim=-1)
 
 
-def latent_attention(h: Tensor, w: Dict[str, Tensor], pre: str, m: dict, eps: float, bf: bool) -> Tensor:
+def latent_attention(h: Tensor, w: Dict[str, Tensor], pre: str, m: dict, eps: float, bf: bool,
+                     probe: dict = None) -> Tensor:
+    """``probe``: a dict that receives the attention weights [heads, T, T] under "weights"."""
     t = h.shape[0]
     H, d, r, dv, kvr = m["heads"], m["dim"], m["rot_dim"], m["vdim"], m["kv_rank"]
     cq = _r(rms_norm(_r(h @ w[pre + "dq"].to(F).t(), bf), w[pre + "dq.norm"], eps), bf)
@@ -81,6 +83,8 @@ def latent_attention(h: Tensor, w: Dict[str, Tensor], pre: str, m: dict, eps: fl
     mask = torch.ones(t, t, dtype=torch.bool).tril()
     s = s.masked_fill(~mask, -math.inf)
     p = torch.softmax(s, dim=-1)
+    if probe is not None:
+        probe["weights"] = p
     o = _r(torch.einsum("hts,shd->thd", p, v), bf).reshape(t, H * dv)
     return o @ w[pre + "o"].to(F).t()
 
@@ -118,11 +122,16 @@ def relu2_expert(h: Tensor, up: Tensor, down: Tensor, bf: bool) -> Tensor:
     return _r(a * a, bf) @ down.to(F).t()
 
 
-def moe_ff(h: Tensor, w: Dict[str, Tensor], pre: str, mlp: dict, bf: bool) -> Tensor:
+def moe_ff(h: Tensor, w: Dict[str, Tensor], pre: str, mlp: dict, bf: bool, margins: list = None) -> Tensor:
+    """``margins`` collects, per token, how far the last chosen logit lies above the best
+    one left out (a small gap: a close call that rounding may decide either way)."""
     E, top = mlp["router"]["experts"], mlp["router"]["top"]
     z = (h.to(torch.float32) @ w[pre + "router"].to(torch.float32).t()
          + w[pre + "router.b"].to(torch.float32)).to(F)
     vals, idx = torch.topk(z, top, dim=-1)
+    if margins is not None and top < E:
+        ranked = torch.sort(z, dim=-1, descending=True).values
+        margins.append(ranked[:, top - 1] - ranked[:, top])
     gate = torch.softmax(vals, dim=-1)
     out = torch.zeros(h.shape[0], w[pre + "e0.down"].shape[0], dtype=F)
     for e in range(E):
@@ -136,9 +145,11 @@ def moe_ff(h: Tensor, w: Dict[str, Tensor], pre: str, mlp: dict, bf: bool) -> Te
 
 
 def forward(cfg: dict, w: Dict[str, Tensor], tokens: Sequence[int], emulate_bf16: bool = False,
-            layers_out: List[Tensor] = None) -> Tensor:
+            layers_out: List[Tensor] = None, probes: Dict[int, dict] = None,
+            margins: list = None) -> Tensor:
     """Logits [T, vocab] (float64) of one whole sequence; ``layers_out`` collects the
-    residual stream after every layer."""
+    residual stream after every layer; ``probes[i]`` receives layer i's attention weights;
+    ``margins`` the routers' gaps per token (see ``moe_ff``)."""
     bf = emulate_bf16
     eps, groups = cfg["norm"]["eps"], cfg["norm"]["groups"]
     x = w["embed"].to(F)[torch.tensor(list(tokens), dtype=torch.long)]
@@ -147,7 +158,8 @@ def forward(cfg: dict, w: Dict[str, Tensor], tokens: Sequence[int], emulate_bf16
         h = _r(grouped_rms_norm(x, w[f"l{i}.norm1"], eps, groups), bf)
         pre = f"l{i}.mix."
         if layer["type"] == "latent_attention":
-            y = latent_attention(h, w, pre, layer["mixer"], eps, bf)
+            y = latent_attention(h, w, pre, layer["mixer"], eps, bf,
+                                 probes.setdefault(i, {}) if probes is not None else None)
         elif layer["type"] == "retention":
             y = retention(h, w, pre, layer["mixer"], eps, bf)
         else:
@@ -157,7 +169,7 @@ def forward(cfg: dict, w: Dict[str, Tensor], tokens: Sequence[int], emulate_bf16
             if mlp["kind"] == "dense":
                 y = y + dense_ff(h, w, f"l{i}.mlp.", bf)
             elif mlp["kind"] == "moe":
-                y = y + moe_ff(h, w, f"l{i}.mlp.", mlp, bf)
+                y = y + moe_ff(h, w, f"l{i}.mlp.", mlp, bf, margins)
             else:
                 raise ValueError(mlp["kind"])
         x = x + y
@@ -165,3 +177,15 @@ def forward(cfg: dict, w: Dict[str, Tensor], tokens: Sequence[int], emulate_bf16
             layers_out.append(x.clone())
     x = _r(grouped_rms_norm(x, w["final.norm"], eps, groups), bf)
     return x @ w["embed"].to(F).t()
+
+
+def greedy_generate(cfg: dict, w: Dict[str, Tensor], prompt: Sequence[int], n_new: int,
+                    emulate_bf16: bool = False) -> List[int]:
+    """The plain loop: the whole sequence again for every new token; ties to the lower id."""
+    tokens, out = list(prompt), []
+    for _ in range(n_new):
+        logits = forward(cfg, w, tokens, emulate_bf16)[-1]
+        best = int(torch.nonzero(logits == logits.max())[0])
+        tokens.append(best)
+        out.append(best)
+    return out

@@ -1,0 +1,316 @@
+"""Nafezen on the GPU against the plain implementation: every mechanism alone, whole
+prompts against token-by-token decoding, portions down to two tokens, unequal batches
+against each request alone, slots and pages used again, far keys and page borders with
+attention made sharp, long decoding, other sizes, greedy generation through the Python
+entry point, and the replay program."""
+import json
+import os
+import random
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+import plain_nafezen as P
+from helpers import TraceBuilder, check_logits, random_tokens, read_step, three_cuts
+from nafezen_models import CONFIGS, ONLY_LATENT, load_weights, make_model, read_config
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+DTYPES = ["float32", "bfloat16"]
+
+
+@pytest.fixture(scope="module")
+def models(tmp_path_factory):
+    out = {name: make_model(str(tmp_path_factory.mktemp(f"nafezen_{name}")), cfg, seed=300 + i)
+           for i, (name, cfg) in enumerate(CONFIGS.items())}
+    out["sharp"] = make_model(str(tmp_path_factory.mktemp("nafezen_sharp")), ONLY_LATENT, seed=77, sharpen=6.0)
+    return out
+
+
+_engines, _plain = {}, {}
+
+
+def engine_for(models, name, dtype):
+    from nnis_b200.engine import Engine
+    if (name, dtype) not in _engines:
+        _engines[(name, dtype)] = Engine.from_dir(models[name], dtype=dtype, max_tokens=64 * 64)
+    return _engines[(name, dtype)]
+
+
+# A router's close call may go either way under bfloat16 rounding, and the token then runs
+# another expert: in bfloat16 a position is compared only where every router of the plain
+# implementation chose with at least this gap between the last logit in and the first out.
+CLOSE_CALL = 0.08
+
+
+def _plain_run(models, name, dtype, tokens):
+    key = (name, dtype, tuple(tokens))
+    if key not in _plain:
+        bf = dtype == "bfloat16"
+        margins = []
+        logits = P.forward(read_config(models[name]), load_weights(models[name], bf), tokens, emulate_bf16=bf,
+                           margins=margins)
+        gap = torch.stack(margins).min(dim=0).values if margins else torch.full((len(tokens),), float("inf"))
+        _plain[key] = (logits, gap)
+    return _plain[key]
+
+
+def plain_logits(models, name, dtype, tokens):
+    return _plain_run(models, name, dtype, tokens)[0]
+
+
+def clear_calls(models, name, dtype, tokens):
+    """Per position: whether the comparison holds there (always in float32)."""
+    gap = _plain_run(models, name, dtype, tokens)[1]
+    return torch.ones_like(gap, dtype=torch.bool) if dtype == "float32" else gap >= CLOSE_CALL
+
+
+def replay_and_check(models, name, dtype, trace, sequences, tmp_path, what):
+    from nnis_b200.engine.replay import replay
+    engine = engine_for(models, name, dtype)
+    out = str(tmp_path / f"out_{name}_{dtype}")
+    replay(engine, trace.lines, out)
+    usage = engine.cache.usage()
+    assert usage["slots_held"] == 0 and not any(usage["pages_held"]), usage
+    engine.cache.check()
+    vocab = read_config(models[name])["vocab"]
+    compared = skipped = 0
+    for step, rows in trace.rows.items():
+        got = read_step(out, step, vocab)
+        assert got.shape[0] == len(rows)
+        keep = [j for j, (rid, pos) in enumerate(rows) if bool(clear_calls(models, name, dtype, sequences[rid])[pos])]
+        compared, skipped = compared + len(keep), skipped + len(rows) - len(keep)
+        if keep:
+            want = torch.stack([plain_logits(models, name, dtype, sequences[rows[j][0]])[rows[j][1]] for j in keep])
+            check_logits(got[keep], want, dtype, f"{what} {name} {dtype} step {step}")
+    assert skipped <= 0.25 * (compared + skipped), (compared, skipped)
+
+
+def run_whole(engine, tokens, want=None):
+    from nnis_b200.engine import SequenceStep
+    slot = engine.acquire_slot()
+    try:
+        return engine.step([SequenceStep(slot, tokens, list(range(len(tokens))) if want is None else want)]).cpu().numpy()
+    finally:
+        engine.release_slot(slot)
+
+
+# ---- kernels of the new mechanisms against plain float32 torch --------------------------
+def test_group_norm_rotation_router_and_head_products():
+    from nnis_b200.csrc import ops
+    dev = torch.device("cuda:0")
+    g = torch.Generator().manual_seed(5)
+    x = torch.randn(37, 90, generator=g)
+    w = torch.randn(90, generator=g)
+    for groups in (1, 3, 5, 90):
+        for dtype in (torch.float32, torch.bfloat16):
+            out = torch.empty(37, 90, dtype=dtype, device=dev)
+            ops.group_rmsnorm(x.to(dev), w.to(dev), 1e-5, groups, out)
+            want = P.grouped_rms_norm(x, w, 1e-5, groups).float()
+            tol = 1e-5 if dtype == torch.float32 else 2e-2
+            assert torch.allclose(out.float().cpu(), want, atol=tol, rtol=tol)
+    rows = torch.tensor([4, 0, 36], dtype=torch.int32, device=dev)
+    out = torch.empty(3, 90, dtype=torch.float32, device=dev)
+    ops.group_rmsnorm(x.to(dev), w.to(dev), 1e-5, 3, out, rows)
+    assert torch.allclose(out.cpu(), P.grouped_rms_norm(x[[4, 0, 36]], w, 1e-5, 3).float(), atol=1e-5)
+    inplace = x.to(dev).clone()
+    ops.group_rmsnorm(inplace, w.to(dev), 1e-5, 5, inplace)
+    assert torch.allclose(inplace.cpu(), P.grouped_rms_norm(x, w, 1e-5, 5).float(), atol=1e-5)
+    # rotation of a part of every head into another layout
+    heads, src_head, length, dims = 3, 14, 10, 6
+    src = torch.randn(9, heads * src_head, generator=g)
+    pos = torch.tensor([0, 1, 2, 70, 500, 3, 4, 5, 100000], dtype=torch.int32)
+    freq = torch.pow(torch.tensor(37.0), -(2 * torch.arange(3, dtype=torch.float32)) / 6.0)
+    dst = torch.zeros(9, heads * 12, device=dev)
+    ops.rope_part(src.to(dev), src_head, 4, dst, 12, 2, pos.to(dev), freq.to(dev), heads, length, dims)
+    part = src.view(9, heads, src_head)[..., 4:].double()
+    ang = pos.float()[:, None] * freq[None, :]
+    c, s = torch.cos(ang).double()[:, None, :], torch.sin(ang).double()[:, None, :]
+    want = torch.cat([part[..., :3] * c - part[..., 3:6] * s, part[..., 3:6] * c + part[..., :3] * s,
+                      part[..., 6:]], -1)
+    got = dst.cpu().view(9, heads, 12)
+    assert torch.allclose(got[..., 2:].double(), want, atol=1e-5) and float(got[..., :2].abs().max()) == 0.0
+    # the router: the top logits, ties to the lower index, softmax over the chosen
+    h = torch.randn(21, 40, generator=g)
+    wr, br = torch.randn(11, 40, generator=g), torch.randn(11, generator=g)
+    wr[7] = wr[2]
+    br[7] = br[2]  # a tie
+    live = torch.zeros(21, dtype=torch.int32, device=dev)
+    for top in (1, 4, 11):
+        ids = torch.empty(21, top, dtype=torch.int32, device=dev)
+        wts = torch.empty(21, top, dtype=torch.float32, device=dev)
+        ops.moe_route(h.to(dev), wr.to(dev), br.to(dev), live, ids, wts, top)
+        z = h.double() @ wr.double().t() + br.double()
+        for n in range(21):
+            order = sorted(range(11), key=lambda e: (-float(z[n, e]), e))[:top]
+            assert ids[n].tolist() == order, (n, top)
+            assert torch.allclose(wts[n].cpu().double(), torch.softmax(z[n, order], 0), atol=1e-5)
+    # one small matrix per head on packed rows
+    for m in (3, 50):
+        a = torch.randn(m, 4 * 9, generator=g)
+        wh = torch.randn(4, 6, 7, generator=g)
+        out = torch.zeros(m, 4 * 8, device=dev)
+        ops.batched_linear(a.to(dev), 9, wh.to(dev), out, 8)
+        want = torch.einsum("mhk,hnk->mhn", a.view(m, 4, 9)[..., :7].double(), wh.double())
+        assert torch.allclose(out.cpu().view(m, 4, 8)[..., :6].double(), want, atol=1e-4)
+
+
+# ---- whole models ------------------------------------------------------------------------------
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["latent", "retention", "moe", "dense"])
+def test_each_mechanism_alone(models, name, dtype, tmp_path):
+    rng = random.Random(11)
+    vocab = read_config(models[name])["vocab"]
+    sequences, trace = {}, TraceBuilder()
+    for i, n in enumerate((1, 2, 3, 64, 65, 131)):  # the first tokens, a page's border
+        sequences[f"w{i}"] = random_tokens(rng, n, vocab)
+        trace.step([(f"w{i}", sequences[f"w{i}"], range(n))], end=[f"w{i}"])
+    toks = sequences["d"] = random_tokens(rng, 75, vocab)  # decoding from the second token on
+    trace.step([("d", toks[:1], [0])])
+    for t in range(1, 75):
+        trace.step([("d", toks[t:t + 1], [0])], end=["d"] if t == 74 else [])
+    replay_and_check(models, name, dtype, trace, sequences, tmp_path, "alone")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["mixed", "odd"])
+def test_whole_last_tokens_and_unequal_batches(models, name, dtype, tmp_path):
+    vocab = read_config(models[name])["vocab"]
+    trace, sequences = three_cuts(random.Random(3), vocab)
+    replay_and_check(models, name, dtype, trace, sequences, tmp_path, "three cuts")
+
+
+@pytest.mark.parametrize("name", ["mixed", "odd"])
+def test_portions_batches_and_reuse_agree_with_each_request_alone(models, name):
+    """float32: the same position's logits whatever the cut, the batch, the slot or the pages."""
+    from nnis_b200.engine import SequenceStep
+    engine = engine_for(models, name, "float32")
+    vocab = read_config(models[name])["vocab"]
+    rng = random.Random(9)
+    prompts = [random_tokens(rng, n, vocab) for n in (200, 3, 67, 130)]
+    alone = [run_whole(engine, p) for p in prompts]
+    scale = max(float(np.abs(a).max()) for a in alone)
+    for p, a in zip(prompts, alone):
+        check_logits(a, plain_logits(models, name, "float32", p), "float32", "alone")
+    # portions of several sizes, down to two tokens and one
+    for cuts in ([2, 2, 60, 1, 64, 71], [64, 64, 64, 8], [199, 1], [1, 199]):
+        slot = engine.acquire_slot()
+        rows, at = [], 0
+        for c in cuts:
+            rows.append(engine.step([SequenceStep(slot, prompts[0][at:at + c], list(range(c)))]).cpu().numpy())
+            at += c
+        engine.release_slot(slot)
+        assert at == 200 and np.abs(np.concatenate(rows) - alone[0]).max() < 2e-5 * scale, cuts
+    # one batch of all four, then the same again in slots and pages that were used before
+    for _ in range(2):
+        slots = [engine.acquire_slot() for _ in prompts]
+        heads = [max(1, len(p) - 20) for p in prompts]
+        got = engine.step([SequenceStep(s, p[:h], list(range(h))) for s, p, h in zip(slots, prompts, heads)]).cpu().numpy()
+        at = 0
+        for i, h in enumerate(heads):
+            assert np.abs(got[at:at + h] - alone[i][:h]).max() < 2e-5 * scale
+            at += h
+        live = list(range(len(prompts)))
+        step = 0
+        while live:  # decoded together; the shorter ones end earlier
+            batch = [SequenceStep(slots[i], prompts[i][heads[i] + step:heads[i] + step + 1], [0]) for i in live]
+            got = engine.step(batch).cpu().numpy()
+            for r, i in enumerate(live):
+                assert np.abs(got[r] - alone[i][heads[i] + step]).max() < 2e-5 * scale, (i, step)
+            step += 1
+            for i in list(live):
+                if heads[i] + step == len(prompts[i]):
+                    engine.release_slot(slots[i])
+                    live.remove(i)
+    assert engine.cache.usage()["slots_held"] == 0
+    engine.cache.check()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_long_decoding_over_page_borders(models, dtype, tmp_path):
+    vocab = read_config(models["mixed"])["vocab"]
+    toks = random_tokens(random.Random(21), 5 + 200, vocab)
+    trace = TraceBuilder()
+    trace.step([("a", toks[:5], [4])])
+    for t in range(5, len(toks)):
+        trace.step([("a", toks[t:t + 1], [0])], end=["a"] if t == len(toks) - 1 else [])
+    replay_and_check(models, "mixed", dtype, trace, {"a": toks}, tmp_path, "long decoding")
+
+
+def test_far_keys_and_page_borders_with_sharp_attention(models, tmp_path):
+    """Query up-projections times six: most of a query's weight lies on one key, and the
+    plain implementation says which.  Among those keys are far ones and ones on both sides
+    of page borders, so an implementation that lost one of them would differ there."""
+    cfg = read_config(models["sharp"])
+    toks = random_tokens(random.Random(8), 400, cfg["vocab"])
+    probes = {}
+    P.forward(cfg, load_weights(models["sharp"], False), toks, probes=probes)
+    weights = probes[0]["weights"]  # [heads, T, T]
+    top, arg = weights.max(dim=-1)
+    queries = torch.arange(400)[None, :].expand_as(arg)
+    strong = top > 0.5
+    assert int(strong.sum()) > 200
+    distance = (queries - arg)[strong]
+    assert int((distance > 256).sum()) >= 5 and int((distance > 128).sum()) >= 20
+    in_page = (arg % 64)[strong & (queries - arg > 64)]
+    assert int((in_page == 63).sum()) >= 1 and int((in_page == 0).sum()) >= 1
+    trace = TraceBuilder()
+    trace.step([("w", toks, range(400))], end=["w"])
+    trace.step([("d", toks[:300], range(300))])
+    for t in range(300, 400):
+        trace.step([("d", toks[t:t + 1], [0])], end=["d"] if t == 399 else [])
+    for dtype in DTYPES:
+        replay_and_check(models, "sharp", dtype, trace, {"w": toks, "d": toks}, tmp_path, "sharp")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_greedy_generation_through_the_entry_point(models, dtype):
+    from nnis_b200 import LLM
+    d = models["mixed"]
+    cfg = read_config(d)
+    bf = dtype == "bfloat16"
+    w = load_weights(d, bf)
+    llm = LLM(d, dtype=dtype, max_tokens=64 * 32, max_batch=3)
+    prompts = [[5, 9, 1, 200, 33], [7], [100, 101, 102, 103, 104, 105, 106, 107, 108], [250, 3], [9] * 70]
+    results = llm.generate(prompts, max_new_tokens=10, stop_token_ids=())
+    for p, r in zip(prompts, results):
+        assert r.ok and r.finish_reason == "length"
+        if not bf:
+            assert r.token_ids == P.greedy_generate(cfg, w, p, 10), (dtype, p)
+        else:  # a bfloat16 near-tie may go either way: every pick must be (nearly) the plain best
+            seq = list(p)
+            for t in r.token_ids:
+                logits = P.forward(cfg, w, seq, emulate_bf16=True)[-1]
+                assert float(logits.max() - logits[t]) <= 0.03 * max(1.0, float(logits.abs().max())), (p, t)
+                seq.append(t)
+    # a session goes on from where generation left it, state and all
+    session = llm.new_session()
+    from nnis_b200 import GenerationConfig
+    ids = session.generate(prompts[0], GenerationConfig(6))
+    more = session.decode_one(17)
+    if not bf:
+        want = P.forward(cfg, w, prompts[0] + ids + [17])[-1]
+        check_logits(np.asarray(more).reshape(1, -1), want[None, :], dtype, "session")
+    assert llm.engine.cache.usage()["slots_held"] <= 1
+
+
+def test_replay_program_runs_a_model_folder(models, tmp_path):
+    cfg = read_config(models["odd"])
+    toks = random_tokens(random.Random(4), 40, cfg["vocab"])
+    trace = TraceBuilder()
+    trace.step([("a", toks[:30], [0, 29]), ("b", toks[:7], [6])])
+    trace.step([("a", toks[30:31], [0]), ("b", toks[7:8], [0])], end=["b"])
+    trace.step([("a", toks[31:32], [])], end=["a"])
+    out = str(tmp_path / "out")
+    r = subprocess.run([os.path.join(ROOT, "bin", "trace_run"), "--model", models["odd"], "--dtype", "float32",
+                        "--out", out, "--max-tokens", "256"], input="\n".join(trace.lines) + "\n",
+                       capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    assert [l for l in r.stdout.splitlines() if l.startswith("done")] == ["done 0", "done 1", "done 2"]
+    assert not os.path.exists(os.path.join(out, "2.f32"))
+    want = plain_logits(models, "odd", "float32", toks)
+    check_logits(read_step(out, 0, cfg["vocab"]), torch.stack([want[0], want[29], want[6]]), "float32", "program")
+    check_logits(read_step(out, 1, cfg["vocab"]), torch.stack([want[30], want[7]]), "float32", "program")
