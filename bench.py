@@ -3,7 +3,7 @@
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
                     [--shape 135m|360m|1.7b] [--batch B] [--context C] [--layers L] [--skip-points]
-                    [--skip-e2e]
+                    [--skip-e2e] [--designs s,m]
 
 A step is one decode step of a batch of 8 sequences whose context ends at 4,096
 tokens (prompt 2,048 + 2,048 decoded); ``value`` is decoded tokens per second,
@@ -235,6 +235,153 @@ def timeline(engine, batch, path, rng, vocab):
                    "projections x staged / products done; attention pages done / ticket taken")
 
 
+# ---------------------------------------------------------------------------
+# --designs: the Nafezen design beside the Llama decoder at equal width and depth
+# ---------------------------------------------------------------------------
+def design_configs(size: str):
+    """(Llama config, Nafezen config) of one width, depth and feed-forward size; the Nafezen
+    layers alternate latent attention with dense and expert feed-forwards and hold one
+    retention layer in four."""
+    width, heads, ff, layers, q_rank, kv_rank, experts, top = {
+        "s": (1024, 16, 2816, 8, 384, 256, 16, 2),
+        "m": (2048, 16, 5632, 8, 768, 512, 32, 4),
+    }[size]
+    dim = width // heads
+    llama = dict(architectures=["LlamaForCausalLM"], model_type="llama", vocab_size=32768, hidden_size=width,
+                 intermediate_size=ff, num_hidden_layers=layers, num_attention_heads=heads,
+                 num_key_value_heads=heads // 4, max_position_embeddings=8192, rms_norm_eps=1e-5,
+                 rope_theta=100000.0, hidden_act="silu", tie_word_embeddings=True, attention_bias=False,
+                 torch_dtype="bfloat16")
+    latent = {"heads": heads, "dim": dim, "rot_dim": dim // 2, "vdim": dim, "q_rank": q_rank, "kv_rank": kv_rank,
+              "rot": {"base": 10000.0, "dims": dim // 2}, "scale": (dim + dim // 2) ** -0.5}
+    ret_heads = max(1, width // 256)
+    retention = {"heads": ret_heads, "dim": 128, "vdim": 256, "rot": {"base": 10000.0, "dims": 128},
+                 "decay": [1.0 - 2.0 ** (-5 - i % 4) for i in range(ret_heads)]}
+    dense = {"kind": "dense", "ff": ff}
+    moe = {"kind": "moe", "router": {"experts": experts, "top": top}, "expert": {"ff": ff // (2 * top)},
+           "shared": {"ff": ff // 2}}
+    pattern = [("latent_attention", latent, dense), ("latent_attention", latent, moe),
+               ("retention", retention, moe), ("latent_attention", latent, dense)]
+    nafezen = {"architecture": "Nafezen", "vocab": 32768, "width": width, "norm": {"eps": 1e-5, "groups": 4},
+               "layers": [{"type": t, "mixer": m, "mlp": f} for t, m, f in (pattern[i % 4] for i in range(layers))]}
+    return llama, nafezen
+
+
+def compare_designs(args) -> int:
+    """Prefill and decode of both designs at each size, with the time of every part of a
+    prompt step (CUDA events around the part, one eager step) against the part's own
+    count of operations; one JSON line per design and size."""
+    import torch
+
+    from nnis_b200 import LLM
+    from nnis_b200.engine import SequenceStep
+    from nnis_b200.engine.decode import GraphDecoder
+    from nnis_b200.weights import write_random_model
+    pk = peaks()
+    rng = random.Random(0)
+    prompt_len, context, batch = 2048, 2048, 8
+
+    def timed(fn, n):
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        start.record()
+        for _ in range(n):
+            fn()
+        end.record()
+        torch.cuda.synchronize()
+        return start.elapsed_time(end) / n
+
+    for size in args.designs.split(","):
+        for name, cfg in zip(("llama", "nafezen"), design_configs(size)):
+            with tempfile.TemporaryDirectory() as tmp:
+                write_random_model(cfg, seed=0, out_dir=tmp, std=1.0, norm_std=0.1, std_by_fan_in=True)
+                llm = LLM(tmp, dtype="bfloat16", device_ordinal=0, max_tokens=batch * (context + 64) + 4 * prompt_len,
+                          max_batch=batch, pipeline_decode=False)
+            engine = llm.engine
+            vocab = engine.spec.vocab_size
+            prompt = [rng.randrange(vocab) for _ in range(prompt_len)]
+
+            def prefill_once():
+                slot = engine.acquire_slot()
+                engine.step([SequenceStep(slot, prompt, [prompt_len - 1])])
+                engine.release_slot(slot)
+            for _ in range(3):
+                prefill_once()
+            prefill_ms = median([timed(prefill_once, 4) for _ in range(REPEATS)])
+            flops = engine.model.step_flops([prompt_len], [0], 1)
+            # every part of one eager prompt step between events of its own
+            parts, marks = {}, []
+            saved = []
+            for block in engine.model.blocks:
+                for part in block.parts():
+                    kind = type(part).__name__
+                    saved.append((part, part.forward))
+
+                    def wrapped(*a, _f=part.forward, _k=kind, _p=part, **kw):
+                        b, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                        b.record()
+                        out = _f(*a, **kw)
+                        e.record()
+                        marks.append((_k, _p, b, e))
+                        return out
+                    part.forward = wrapped
+            import nnis_b200.engine.engine as engine_module
+            floor = engine_module.GRAPH_MIN_TOKENS
+            engine_module.GRAPH_MIN_TOKENS = 1 << 30  # eager: the events must be in the stream
+            try:
+                for rep in range(3):
+                    marks.clear()
+                    prefill_once()
+                torch.cuda.synchronize()
+            finally:
+                engine_module.GRAPH_MIN_TOKENS = floor
+                for part, fwd in saved:
+                    part.forward = fwd
+            for kind, part, b, e in marks:
+                entry = parts.setdefault(kind, {"ms": 0.0, "flops": 0.0, "calls": 0})
+                entry["ms"] += b.elapsed_time(e)
+                entry["flops"] += part.step_flops([prompt_len], [0])
+                entry["calls"] += 1
+            for entry in parts.values():
+                entry["frac_of_bf16_peak"] = round(entry["flops"] / (entry["ms"] * 1e-3) / (pk["bf16_tflops"] * 1e12), 4) \
+                    if entry["ms"] > 0 else None
+                entry["ms"] = round(entry["ms"], 3)
+            # decoding: batch 8, contexts ending at 2,048, one CUDA graph a step
+            steps, warm = 64, 8
+            begin = context - steps - warm
+            slots = [engine.acquire_slot() for _ in range(batch)]
+            for s in slots:
+                engine.step([SequenceStep(s, [rng.randrange(vocab) for _ in range(begin)], [])])
+            dec = GraphDecoder(engine, batch, context)
+            engine.cache.reserve(slots, [context] * batch)
+            regions = []
+            snaps = [engine.snapshot(s) for s in slots]
+            for rep in range(REPEATS):
+                for r, s in enumerate(slots):
+                    dec.set_row(r, s, rng.randrange(vocab), begin)
+                dec.capture()
+                for _ in range(warm):
+                    dec.launch()
+                regions.append(timed(dec.launch, steps))
+            step_ms = median(regions)
+            step_bytes = engine.model.parameter_bytes() + batch * (context - steps / 2) * engine.cache.kv_bytes_per_token()
+            for s in slots:
+                engine.release_slot(s)
+            print(json.dumps({
+                "design": name, "size": size, "width": engine.spec.hidden_size, "layers": len(engine.spec.layers),
+                "weights_read_per_step_mb": round(engine.model.parameter_bytes() / 1e6, 1),
+                "prefill": {"tokens": prompt_len, "ms": round(prefill_ms, 3), "tok_s": round(prompt_len / (prefill_ms * 1e-3)),
+                            "frac_of_bf16_peak": round(flops / (prefill_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)},
+                "prefill_parts": parts,
+                "decode": {"batch": batch, "context": context, "ms_per_step": round(step_ms, 4),
+                           "tok_s": round(batch / (step_ms * 1e-3)), "launches_per_step": dec.launches_per_step,
+                           "frac_of_hbm": round(step_bytes / (step_ms * 1e-3) / 1e9 / pk["hbm_gbs"], 4)},
+                "peaks": pk["source"], "dtype": "bf16", "data": "synthetic (seeded random weights and token ids)"}))
+            del llm, engine, dec
+            torch.cuda.empty_cache()
+    return 0
+
+
 def main() -> int:
     global CONTEXT
     ap = argparse.ArgumentParser()
@@ -254,7 +401,12 @@ def main() -> int:
                          "with --batch 0, of the 2,048-token prompt step")
     ap.add_argument("--shape", default="135m", choices=sorted(SHAPES),
                     help="layer sizes: the SmolLM2-135M shape (the benchmark) or a larger one of the family")
+    ap.add_argument("--designs", metavar="SIZES", default=None,
+                    help="instead of the benchmark: the Nafezen design beside the Llama decoder at equal "
+                         "width and depth, sizes 's' and/or 'm' with commas: prefill, its parts, decoding")
     args = ap.parse_args()
+    if args.designs:
+        return compare_designs(args)
     CONTEXT = max(args.context, 64)
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":

@@ -1096,3 +1096,44 @@ def moe_experts(h: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor, ids: 
     _check(_lib().nnis_moe_experts(_ptr(h), _ptr(w_up), _ptr(w_down), _ptr(ids), _ptr(weights),
                                    _ptr(token_pos), _ptr(act), _ptr(residual), n, width, ff, top,
                                    code_of(h.dtype), _stream()), "moe_experts", 2)
+
+
+LATENT_MMA = 0 if os.environ.get("NNIS_LATENT_MMA", "1") == "0" else 1
+LATENT_TILE_ROWS = 64  # stacked (token, head) rows per CTA of attention_latent_mma
+
+
+def attention_latent_mma_takes(dk: int, dv: int, page_size: int) -> bool:
+    """Whether the tensor-core latent attention runs these sizes (bfloat16 only)."""
+    return bool(LATENT_MMA) and bool(_lib().nnis_attention_latent_mma_takes(dk, dv, page_size))
+
+
+def latent_tiles(counts, heads: int):
+    """The work list of ``attention_latent_mma`` for a prompt step: (sequence, first stacked
+    row) per 64 rows of each sequence's tokens * heads rows."""
+    import numpy as np
+    tiles = [(i, r0) for i, c in enumerate(counts) for r0 in range(0, int(c) * heads, LATENT_TILE_ROWS)]
+    return np.asarray(tiles, dtype=np.int32).reshape(-1, 2)
+
+
+def attention_latent_mma(q: torch.Tensor, cache: torch.Tensor, tiles: Optional[torch.Tensor],
+                         seq_first_row: Optional[torch.Tensor], seq_start: Optional[torch.Tensor],
+                         seq_count: Optional[torch.Tensor], token_pos: torch.Tensor, token_seq: torch.Tensor,
+                         page_table: torch.Tensor, out: torch.Tensor, heads: int, dv: int, scale: float,
+                         n_splits: int = 1, partial: Optional[torch.Tensor] = None) -> None:
+    """``attention_latent`` on the tensor cores (bfloat16).  With ``tiles`` (``latent_tiles``) a
+    prompt step; without, every row is one token of a sequence of its own."""
+    _cuda(q, cache, tiles, seq_first_row, seq_start, seq_count, token_pos, token_seq, page_table, out, partial)
+    n = out.shape[0]
+    pages, one, page_size, dk = cache.shape
+    _need(q.dtype == cache.dtype == out.dtype == torch.bfloat16, "attention_latent_mma: bfloat16")
+    _need(one == 1 and q.shape[1] == heads * dk and out.shape[1] == heads * dv, "attention_latent_mma: shapes")
+    _need(attention_latent_mma_takes(dk, dv, page_size), "attention_latent_mma: sizes not taken")
+    _need(pages * page_size < 2 ** 31, "attention_latent_mma: the cache has too many rows")
+    if n_splits > 1:
+        _need(partial is not None and partial.dtype == torch.float32
+              and partial.numel() >= n * heads * n_splits * (dv + 2), "attention_latent_mma: partial scratch")
+    _check(_lib().nnis_attention_latent_mma(
+        _ptr(q), _ptr(cache), _ptr(tiles), tiles.shape[0] if tiles is not None else 0, _ptr(seq_first_row),
+        _ptr(seq_start), _ptr(seq_count), _ptr(token_pos), _ptr(token_seq), _ptr(page_table),
+        page_table.shape[1], _ptr(out), _ptr(partial), n, heads, dk, dv, page_size, ctypes.c_float(scale),
+        n_splits, _stream()), "attention_latent_mma", 2 if n_splits > 1 else 1)

@@ -26,7 +26,7 @@ from typing import Dict, Mapping, Optional
 
 import torch
 
-from ..cache import KVRequest, KVView
+from ..cache import PAGE_SIZE, KVRequest, KVView
 from ..csrc import ops
 from ..weights.loader import WeightSpec
 from .base import MIXERS, POSITIONS, Part
@@ -109,6 +109,28 @@ class LatentAttention(Part):
         keys = sum(c * st + c * (c + 1) // 2 for c, st in zip(counts, starts))
         return 2.0 * tokens * per_token + 2.0 * H * (self.row + self.kv_rank) * keys
 
+    # -- work lists ---------------------------------------------------------
+    def _tiles_name(self) -> str:
+        return f"latent_mma/heads{self.heads}"
+
+    def _tensor_cores(self) -> bool:
+        return self.dtype == torch.bfloat16 and ops.attention_latent_mma_takes(self.row, self.kv_rank, PAGE_SIZE)
+
+    def step_tables(self, counts, starts, have=()):
+        """The tiles of the tensor-core kernel for a prompt step: 64 stacked (token, head)
+        rows each; the same for every layer with this number of heads."""
+        if not self._tensor_cores() or self._tiles_name() in have:
+            return {}
+        return {self._tiles_name(): ops.latent_tiles(counts, self.heads)}
+
+    def _decode_splits(self, ctx, n: int) -> int:
+        """Slices of the key range in a step of single tokens: enough CTAs for two per SM,
+        at least two pages a slice."""
+        ctas = n * -(-self.heads // ops.LATENT_TILE_ROWS) * -(-self.kv_rank // 128)
+        pages = max(1, -(-ctx.max_context // PAGE_SIZE))
+        want = -(-2 * ops.sm_count(self.device) // max(1, ctas * max(1, ctx.share)))
+        return int(max(1, min(want, pages // 2, 64)))
+
     # -- run --------------------------------------------------------------
     def forward(self, x: torch.Tensor, ctx, residual: torch.Tensor, cache: KVView) -> None:
         n = residual.shape[0]
@@ -128,11 +150,24 @@ class LatentAttention(Part):
             ops.rope_part(q, self.dim + self.rot, self.dim, q_lat, self.row, self.kv_rank, ctx.token_pos,
                           freq, H, self.rot, self.position.dims)
         o_lat = ws.get("latent_o", (n, H * self.kv_rank), self.dtype)
-        splits = ctx.attention_splits(n * H)
-        partial = ws.get("attn_partial", (n * H * splits * (self.kv_rank + 2),), torch.float32) \
-            if splits > 1 else None
-        ops.attention_latent(q_lat, cache.k, ctx.token_pos, ctx.token_seq, table, o_lat, H, self.kv_rank,
-                             self.scale, splits, partial)
+        tiles = ctx.tables.get(self._tiles_name())
+        if self._tensor_cores() and (ctx.decode or tiles is not None):
+            splits = self._decode_splits(ctx, n) if ctx.decode else 1
+            partial = ws.get("attn_partial", (n * H * splits * (self.kv_rank + 2),), torch.float32) \
+                if splits > 1 else None
+            if ctx.decode:
+                ops.attention_latent_mma(q_lat, cache.k, None, None, None, None, ctx.token_pos, ctx.token_seq,
+                                         table, o_lat, H, self.kv_rank, self.scale, splits, partial)
+            else:
+                ops.attention_latent_mma(q_lat, cache.k, tiles, ctx.seq_first_row, ctx.seq_start,
+                                         ctx.seq_count, ctx.token_pos, ctx.token_seq, table, o_lat, H,
+                                         self.kv_rank, self.scale)
+        else:
+            splits = ctx.attention_splits(n * H)
+            partial = ws.get("attn_partial", (n * H * splits * (self.kv_rank + 2),), torch.float32) \
+                if splits > 1 else None
+            ops.attention_latent(q_lat, cache.k, ctx.token_pos, ctx.token_seq, table, o_lat, H, self.kv_rank,
+                                 self.scale, splits, partial)
         attn = ws.get("attn", (n, H * self.vdim), self.dtype)
         ops.batched_linear(o_lat, self.kv_rank, self.w_uv, attn, self.vdim)
         linear(attn, self.w_o, None, residual, ADD_F32, ws)
