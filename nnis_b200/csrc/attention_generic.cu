@@ -152,6 +152,7 @@ static int launch_attention(const void* q, int q_stride, const void* k_cache, co
 // The merge alone, for kernels that write the same partial records.
 extern "C" int nnis_attention_merge_bf16(const float* partial, void* out, long long n_rows, int d,
                                          int n_splits, cudaStream_t stream) {
+    if (n_splits > 64) return NNIS_ERR_UNSUPPORTED;
     nnis::attn_merge_kernel<nnis::bf16><<<(unsigned)((n_rows + 3) / 4), 128, 0, stream>>>(
         partial, (nnis::bf16*)out, (size_t)n_rows, d, n_splits);
     NNIS_RETURN_LAUNCH();
@@ -168,7 +169,7 @@ NNIS_API int nnis_attention_generic(const void* q, int q_stride, const void* k_c
         n_splits <= 0 || window < 0)
         return NNIS_ERR_ARGUMENT;
     if (d <= 0 || d % 2 || d > 256) return NNIS_ERR_UNSUPPORTED;
-    if (nq > 65535 || n_splits > 65535) return NNIS_ERR_UNSUPPORTED;
+    if (nq > 65535 || n_splits > 64) return NNIS_ERR_UNSUPPORTED;  // (the merge takes 64 slices)
     if (n_splits > 1 && !partial) return NNIS_ERR_ARGUMENT;
     if (dtype == NNIS_DTYPE_F32)
         return nnis::launch_attention<float>(q, q_stride, k_cache, v_cache, token_pos, token_seq,

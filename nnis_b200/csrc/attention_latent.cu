@@ -218,7 +218,7 @@ NNIS_API int nnis_attention_latent(const void* q, const void* cache, const int* 
     if (n_tokens <= 0 || heads <= 0 || dk <= 0 || dv <= 0 || dv > dk || page_size <= 0 ||
         table_cols <= 0 || n_splits <= 0)
         return NNIS_ERR_ARGUMENT;
-    if (dv > 512 || dk > 2048 || heads > 65535 || n_splits > 65535) return NNIS_ERR_UNSUPPORTED;
+    if (dv > 512 || dk > 2048 || heads > 65535 || n_splits > 64) return NNIS_ERR_UNSUPPORTED;
     if (n_splits > 1 && !partial) return NNIS_ERR_ARGUMENT;
     if (dtype == NNIS_DTYPE_F32)
         return launch_latent<float>(q, cache, token_pos, token_seq, page_table, table_cols, out, partial,

@@ -281,7 +281,7 @@ NNIS_API int nnis_attention_latent_mma(const void* q, const void* cache, const i
     const int dkp = (dk + 63) / 64 * 64;
     const int tiles_per_token = (heads + kLatRows - 1) / kLatRows;
     const int chunks = (dv + kLatChunk - 1) / kLatChunk;
-    if (chunks > 65535 || n_splits > 65535) return NNIS_ERR_UNSUPPORTED;
+    if (chunks > 65535 || n_splits > 64) return NNIS_ERR_UNSUPPORTED;
     dim3 grid(tiles ? n_tiles : n_tokens * tiles_per_token, chunks, n_splits);
     const int stages = latent_mma_smem(dk, 3) <= 100 * 1024 ? 3 : 2;
     const size_t smem = latent_mma_smem(dk, stages);

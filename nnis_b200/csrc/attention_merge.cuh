@@ -9,30 +9,46 @@
 
 namespace nnis {
 
-// Merge the splits of one (token, head) in ascending order of split.
+// A warp per (token, head); at most 64 slices.  The slices' weights exp(m_s - m) / l are
+// worked out once (lane s holds slices s and s + 32), then every output value is one
+// weighted sum over the slices, in ascending order of slice.
 template <typename T>
-__global__ void attn_merge_kernel(const float* __restrict__ partial, T* __restrict__ out,
-                                  size_t n_rows, int d, int n_splits) {
-    size_t row = (size_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-    int lane = threadIdx.x & 31;
+__global__ void __launch_bounds__(128)
+attn_merge_kernel(const float* __restrict__ partial, T* __restrict__ out, size_t n_rows, int d,
+                  int n_splits) {
+    __shared__ float share[4][64];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    size_t row = (size_t)blockIdx.x * 4 + warp;
     if (row >= n_rows) return;
     const float* rec = partial + row * n_splits * (size_t)(d + 2);
+    float ms[2], ls[2];
     float m = -FLT_MAX;
-    for (int s = 0; s < n_splits; ++s)
-        if (rec[(size_t)s * (d + 2) + 1] > 0.f) m = fmaxf(m, rec[(size_t)s * (d + 2)]);
-    float l = 0.f;
-    for (int s = 0; s < n_splits; ++s) {
-        float ls = rec[(size_t)s * (d + 2) + 1];
-        if (ls > 0.f) l += ls * expf(rec[(size_t)s * (d + 2)] - m);
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+        int s = lane + 32 * k;
+        ms[k] = s < n_splits ? rec[(size_t)s * (d + 2)] : 0.f;
+        ls[k] = s < n_splits ? rec[(size_t)s * (d + 2) + 1] : 0.f;
+        if (ls[k] > 0.f) m = fmaxf(m, ms[k]);
     }
-    float inv = l > 0.f ? 1.0f / l : 0.f;
+    m = warp_max(m);
+    float l = 0.f;
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+        ms[k] = ls[k] > 0.f ? expf(ms[k] - m) : 0.f;
+        l += ls[k] * ms[k];
+    }
+    l = warp_sum(l);
+    const float inv = l > 0.f ? 1.0f / l : 0.f;
+    share[warp][lane] = ms[0] * inv;
+    share[warp][lane + 32] = ms[1] * inv;
+    __syncwarp();
     for (int i = lane; i < d; i += 32) {
         float o = 0.f;
         for (int s = 0; s < n_splits; ++s) {
-            float ls = rec[(size_t)s * (d + 2) + 1];
-            if (ls > 0.f) o += rec[(size_t)s * (d + 2) + 2 + i] * expf(rec[(size_t)s * (d + 2)] - m);
+            float w = share[warp][s];
+            if (w > 0.f) o = fmaf(w, rec[(size_t)s * (d + 2) + 2 + i], o);
         }
-        out[row * d + i] = from_float<T>(o * inv);
+        out[row * d + i] = from_float<T>(o);
     }
 }
 

@@ -212,9 +212,10 @@ group_rmsnorm_kernel(const float* x, const int* __restrict__ rows,
 }
 
 // ---------------------------------------------------------------------------
-// out[n, i] = relu(u[n, i])^2 (* sigmoid(u[n, inter]) when `gated`): the
-// activation of an expert whose row of u carries, as its last column, the logit
-// of a gate that scales the expert's whole output.  u float32 [n, inter + gated].
+// out[n, i] = relu(u[n, i])^2 (* sigmoid(u[n, inter]) when `gated` > 0): the
+// activation of an expert whose row of u carries, in column `inter`, the logit
+// of a gate that scales the expert's whole output.  u float32 [n, inter + gated]
+// (`gated` columns beyond the activation's: the gate, then padding).
 // ---------------------------------------------------------------------------
 template <typename T>
 __global__ void relu2_gate_kernel(const float* __restrict__ u, T* __restrict__ out, size_t n_rows,
@@ -380,7 +381,7 @@ NNIS_API int nnis_group_rmsnorm(const float* x, const int* rows, const float* w,
 
 NNIS_API int nnis_relu2_gate(const float* u, void* out, int out_dtype, long long n_rows, int inter,
                              int gated, cudaStream_t stream) {
-    if (n_rows <= 0 || inter <= 0 || (gated != 0 && gated != 1)) return NNIS_ERR_ARGUMENT;
+    if (n_rows <= 0 || inter <= 0 || gated < 0) return NNIS_ERR_ARGUMENT;
     size_t total = (size_t)n_rows * inter;
     unsigned blocks = (unsigned)((total + 255) / 256);
     if (out_dtype == NNIS_DTYPE_F32)

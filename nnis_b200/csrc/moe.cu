@@ -2,7 +2,7 @@
 // feed-forward layers W_down act(W_up h), act = relu^2, and the token's output is
 // the sum of theirs weighted by a softmax over the chosen logits only.
 //
-//   moe_route   logits z = W_r h + b in float32 (a warp per token), the `top` largest
+//   moe_route   logits z = W_r h + b in float32 (a CTA per token, a warp per expert), the `top` largest
 //               (ties to the lower index), softmax over those -> ids, weights
 //   moe_up      act[n, s, :] = relu(W_up[id[n, s]] h_n)^2: a warp per output feature
 //   moe_down    residual[n, :] += sum_s weight[n, s] W_down[id[n, s]] act[n, s, :], the
@@ -17,34 +17,33 @@
 namespace nnis {
 
 template <typename T>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(256)
 moe_route_kernel(const T* __restrict__ h, const float* __restrict__ wr, const float* __restrict__ br,
                  const int* __restrict__ token_pos, int* __restrict__ ids,
                  float* __restrict__ weights, int n_tokens, int width, int experts, int top) {
-    extern __shared__ float z_smem[];
-    int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    int n = blockIdx.x * 4 + warp;
-    if (n >= n_tokens) return;
+    extern __shared__ float z[];  // [experts]
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int n = blockIdx.x;
     int* id = ids + (size_t)n * top;
     float* wt = weights + (size_t)n * top;
     if (token_pos[n] < 0) {
-        for (int s = lane; s < top; s += 32) {
+        for (int s = threadIdx.x; s < top; s += 256) {
             id[s] = 0;
             wt[s] = 0.f;
         }
         return;
     }
-    float* z = z_smem + (size_t)warp * experts;
     const T* x = h + (size_t)n * width;
-    for (int e = 0; e < experts; ++e) {
+    for (int e = warp; e < experts; e += 8) {  // a warp per expert, eight at a time
         const float* w = wr + (size_t)e * width;
         float acc = 0.f;
         for (int i = lane; i < width; i += 32) acc = fmaf(w[i], to_float(x[i]), acc);
         acc = warp_sum(acc);
         if (lane == 0) z[e] = acc + (br ? br[e] : 0.f);
     }
-    __syncwarp();
-    // the `top` largest, one after another; lanes share the search
+    __syncthreads();
+    if (warp != 0) return;
+    // the `top` largest, one after another; the lanes of one warp share the search
     float first = 0.f, total = 0.f;
     for (int s = 0; s < top; ++s) {
         float best = -FLT_MAX;
@@ -131,14 +130,14 @@ NNIS_API int nnis_moe_route(const void* h, const float* wr, const float* br, con
     if (n_tokens <= 0 || width <= 0 || experts <= 0 || top <= 0 || top > experts || !h || !wr || !ids ||
         !weights || !token_pos)
         return NNIS_ERR_ARGUMENT;
-    size_t smem = 4 * (size_t)experts * sizeof(float);
+    size_t smem = (size_t)experts * sizeof(float);
     if (smem > 48 * 1024) return NNIS_ERR_UNSUPPORTED;
-    unsigned blocks = (unsigned)((n_tokens + 3) / 4);
+    unsigned blocks = (unsigned)n_tokens;
     if (dtype == NNIS_DTYPE_F32)
-        moe_route_kernel<float><<<blocks, 128, smem, stream>>>((const float*)h, wr, br, token_pos, ids,
+        moe_route_kernel<float><<<blocks, 256, smem, stream>>>((const float*)h, wr, br, token_pos, ids,
                                                                weights, n_tokens, width, experts, top);
     else if (dtype == NNIS_DTYPE_BF16)
-        moe_route_kernel<bf16><<<blocks, 128, smem, stream>>>((const bf16*)h, wr, br, token_pos, ids,
+        moe_route_kernel<bf16><<<blocks, 256, smem, stream>>>((const bf16*)h, wr, br, token_pos, ids,
                                                               weights, n_tokens, width, experts, top);
     else
         return NNIS_ERR_UNSUPPORTED;

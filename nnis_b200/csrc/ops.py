@@ -929,6 +929,9 @@ def trace_end():
 # ---------------------------------------------------------------------------
 # norm in groups, per-head products, latent attention, retention, experts
 # ---------------------------------------------------------------------------
+# grouped products on the tensor cores (experts of prompt steps, per-head products of many rows)
+MOE_GROUPED = 0 if os.environ.get("NNIS_MOE_GROUPED", "1") == "0" else 1
+
 def group_rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, groups: int, out: torch.Tensor,
                   rows: Optional[torch.Tensor] = None) -> None:
     """out[r] = x[rows[r]] (or x[r]) with each of ``groups`` equal runs divided by its own
@@ -946,14 +949,14 @@ def group_rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, groups: int
                                      width, groups, ctypes.c_float(eps), _stream()), "group_rmsnorm")
 
 
-def relu2_gate(u: torch.Tensor, out: torch.Tensor, gated: bool) -> None:
-    """out = relu(u[:, :I])^2, times sigmoid(u[:, I]) when ``gated``; u float32 [n, I + gated]."""
+def relu2_gate(u: torch.Tensor, out: torch.Tensor) -> None:
+    """out = relu(u[:, :I])^2 for out [n, I]; when u has more columns than that, times
+    sigmoid(u[:, I]) (the columns after the gate's are padding)."""
     _cuda(u, out)
     n, inter = out.shape
-    _need(u.dtype == torch.float32 and tuple(u.shape) == (n, inter + int(gated)),
-          "u: float32 [n, inter + gated]")
+    _need(u.dtype == torch.float32 and u.shape[0] == n and u.shape[1] >= inter, "u: float32 [n, >= inter]")
     _check(_lib().nnis_relu2_gate(_ptr(u), _ptr(out), code_of(out.dtype), ctypes.c_longlong(n), inter,
-                                  int(gated), _stream()), "relu2_gate")
+                                  u.shape[1] - inter, _stream()), "relu2_gate")
 
 
 def rope_part(src: torch.Tensor, src_head: int, src_off: int, dst: torch.Tensor, dst_head: int,
@@ -988,6 +991,14 @@ def batched_linear(a: torch.Tensor, a_head: int, w: torch.Tensor, out: torch.Ten
     _need(k <= a_head and (heads - 1) * a_head + k <= a.shape[1], "batched_linear: K lies outside a's heads")
     _need(n <= out_head and (heads - 1) * out_head + n <= out.shape[1],
           "batched_linear: N lies outside out's heads")
+    if a.dtype == torch.bfloat16 and m > 16 and MOE_GROUPED and k % 8 == 0 and a.shape[1] % 8 == 0 \
+            and a_head % 8 == 0:
+        # many rows: 64 x 64 tiles on the tensor cores (the grouped products' kernel)
+        _check(_lib().nnis_batched_linear_mma(_ptr(a), ctypes.c_longlong(a.shape[1]), ctypes.c_longlong(a_head),
+                                              _ptr(w), _ptr(out), ctypes.c_longlong(out.shape[1]),
+                                              ctypes.c_longlong(out_head), heads, m, n, k, _stream()),
+               "batched_linear_mma")
+        return
     _check(_lib().nnis_batched_linear(_ptr(a), ctypes.c_longlong(a.shape[1]), ctypes.c_longlong(a_head),
                                       _ptr(w), _ptr(out), ctypes.c_longlong(out.shape[1]),
                                       ctypes.c_longlong(out_head), heads, m, n, k, code_of(a.dtype),
@@ -1137,3 +1148,39 @@ def attention_latent_mma(q: torch.Tensor, cache: torch.Tensor, tiles: Optional[t
         _ptr(seq_start), _ptr(seq_count), _ptr(token_pos), _ptr(token_seq), _ptr(page_table),
         page_table.shape[1], _ptr(out), _ptr(partial), n, heads, dk, dv, page_size, ctypes.c_float(scale),
         n_splits, _stream()), "attention_latent_mma", 2 if n_splits > 1 else 1)
+
+
+
+
+def moe_grouped_takes(width: int, ff: int, experts: int) -> bool:
+    """Whether the grouped tensor-core products run these sizes (bfloat16, prompt steps)."""
+    return bool(MOE_GROUPED) and bool(_lib().nnis_moe_grouped_takes(width, ff, experts))
+
+
+def moe_grouped_tiles(n_pairs: int, experts: int) -> int:
+    return int(_lib().nnis_moe_grouped_tiles(ctypes.c_longlong(n_pairs), experts))
+
+
+def moe_grouped(h: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor, ids: torch.Tensor,
+                weights: torch.Tensor, perm: torch.Tensor, place: torch.Tensor, tile_expert: torch.Tensor,
+                act: torch.Tensor, y: torch.Tensor, residual: torch.Tensor, top: int) -> None:
+    """``moe_experts`` for many tokens: pairs sorted by expert, two grouped products on the
+    tensor cores, the chosen experts' outputs added in the router's order.  Every row of
+    ``h`` is a token (no padding rows).  Scratch sizes: see ``moe_grouped_tiles``."""
+    _cuda(h, w_up, w_down, ids, weights, perm, place, tile_expert, act, y, residual)
+    n, width = h.shape
+    experts, ff, _ = w_up.shape
+    tiles = moe_grouped_tiles(n * top, experts)
+    _need(h.dtype == w_up.dtype == w_down.dtype == act.dtype == torch.bfloat16, "moe_grouped: bfloat16")
+    _need(tuple(w_up.shape) == (experts, ff, width) and tuple(w_down.shape) == (experts, width, ff),
+          "moe_grouped: stacked weights")
+    _need(moe_grouped_takes(width, ff, experts), "moe_grouped: sizes not taken")
+    _need(perm.dtype == place.dtype == tile_expert.dtype == ids.dtype == torch.int32
+          and perm.numel() >= tiles * 64 and place.numel() >= n * top and tile_expert.numel() >= tiles,
+          "moe_grouped: int32 scratch")
+    _need(act.numel() >= tiles * 64 * ff and y.dtype == torch.float32 and y.numel() >= tiles * 64 * width,
+          "moe_grouped: act and y scratch")
+    _need(residual.dtype == torch.float32 and tuple(residual.shape) == (n, width), "moe_grouped: residual")
+    _check(_lib().nnis_moe_grouped(_ptr(h), _ptr(w_up), _ptr(w_down), _ptr(ids), _ptr(weights), _ptr(perm),
+                                   _ptr(place), _ptr(tile_expert), _ptr(act), _ptr(y), _ptr(residual), n, width,
+                                   ff, experts, top, _stream()), "moe_grouped", 4)

@@ -7,8 +7,9 @@
 //
 //   retention_scan   a CTA per (sequence, head, 32 columns of vdim) walks the step's
 //                    tokens of that sequence in order; warp w holds rows w, w+8, ...
-//                    of the state tile in registers.  Serves prompts, later chunks
-//                    (the state says where it stands) and single tokens.
+//                    of the state tile in registers.  Steps of single tokens.
+//   retention_chunk  prompts and later chunks of them (the state says where a sequence
+//                    stands): 32 tokens at a time, see below.
 //   retention_gate   o / rms(o) per head, times silu(g), rounded once.
 //
 // Packed input rows: [q (H dim) | k (H dim) | v (H vdim) | g (H vdim)].
@@ -103,6 +104,160 @@ retention_scan_kernel(const T* __restrict__ qkvg, const float* __restrict__ freq
     }
 }
 
+// Prompts: the same recurrence a chunk of 32 tokens at a time.  Within a chunk, with
+// A[i][j] = (q_i . k_j) g^(i-j) for j <= i:
+//     o_i = sum_j A[i][j] v_j + g^(i+1) S^T q_i        S <- g^C S + sum_j g^(C-1-j) k_j v_j^T
+// (C tokens in the chunk, S the state before it), all in float32 on the CUDA cores.  A CTA
+// owns (sequence, head, 32 columns of vdim) and walks the chunks in order with its tile of
+// S in shared memory; q and k of the chunk are rotated once into shared memory.
+constexpr int kRetChunk = 32;
+
+// DR4: dim / 32 (the kernel takes dim = 32, 64, 128, 256; a warp owns dim / 8 rows of the
+// state in the update).  The three products are tiled in registers: 2 x 2 entries of A per
+// thread, four rows of the output per thread, dim / 8 rows of the state per thread, with
+// q and k read as float4 along dim.
+template <typename T, int DR4>
+__global__ void __launch_bounds__(256)
+retention_chunk_kernel(const T* __restrict__ qkvg, const float* __restrict__ freq,
+                       const float* __restrict__ decay, float* __restrict__ state,
+                       const int* __restrict__ seq_slots, const int* __restrict__ seq_first_row,
+                       const int* __restrict__ seq_start, const int* __restrict__ seq_count,
+                       float* __restrict__ o_raw, int heads, int vdim, int rot_dims) {
+    constexpr int C = kRetChunk, dim = 32 * DR4, ld = dim + 4, DR = 4 * DR4;
+    extern __shared__ __align__(16) float smem[];
+    float* qs = smem;                  // [C][dim + 4]
+    float* ks = qs + C * ld;           // [C][dim + 4]
+    float* Ss = ks + C * ld;           // [dim][32]
+    float* As = Ss + dim * 32;         // [C][C + 1]
+    float* vs = As + C * (C + 1);      // [C][32]
+    float* pw = vs + C * 32;           // [C + 1]: g^n
+    const int unit = blockIdx.x, h = blockIdx.y;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, tid = threadIdx.x;
+    const int col = blockIdx.z * 32 + lane;
+    const int first = seq_first_row[unit], start = seq_start[unit], count = seq_count[unit];
+    if (count <= 0) return;
+    const bool live = col < vdim;
+    const float g = decay[h];
+    const float k_scale = 1.0f / sqrtf((float)dim);
+    float* S = state + (((size_t)seq_slots[unit] * heads + h) * dim) * vdim;
+    for (int d = warp; d < dim; d += 8) Ss[d * 32 + lane] = live ? S[(size_t)d * vdim + col] : 0.f;
+    for (int it = tid; it < 2 * C * ld; it += 256) qs[it] = 0.f;  // (rows beyond a short chunk)
+    if (tid == 0) {
+        float p = 1.f;
+        for (int n = 0; n <= C; ++n) {
+            pw[n] = p;
+            p *= g;
+        }
+    }
+    const size_t row_len = (size_t)2 * heads * dim + (size_t)2 * heads * vdim;
+    const int half = rot_dims >> 1, per_tok = dim - half;
+    for (int t0 = 0; t0 < count; t0 += C) {
+        const int cnt = min(C, count - t0);
+        __syncthreads();  // the chunk before is done with qs, ks, vs, As; Ss is up to date
+        for (int it = tid; it < cnt * per_tok; it += 256) {
+            int i = it / per_tok, j = it - i * per_tok;
+            const T* row = qkvg + (size_t)(first + t0 + i) * row_len;
+            const T* qh = row + (size_t)h * dim;
+            const T* kh = row + (size_t)heads * dim + (size_t)h * dim;
+            if (j < half) {
+                float ang = (float)(start + t0 + i) * freq[j];
+                float c = cosf(ang), sn = sinf(ang);
+                float u = to_float(qh[j]), v = to_float(qh[j + half]);
+                qs[i * ld + j] = u * c - v * sn;
+                qs[i * ld + j + half] = v * c + u * sn;
+                u = to_float(kh[j]);
+                v = to_float(kh[j + half]);
+                ks[i * ld + j] = (u * c - v * sn) * k_scale;
+                ks[i * ld + j + half] = (v * c + u * sn) * k_scale;
+            } else {
+                qs[i * ld + j + half] = to_float(qh[j + half]);
+                ks[i * ld + j + half] = to_float(kh[j + half]) * k_scale;
+            }
+        }
+        for (int it = tid; it < C * 32; it += 256) {
+            int i = it >> 5;
+            float v = 0.f;
+            if (i < cnt && live)
+                v = to_float(qkvg[(size_t)(first + t0 + i) * row_len + (size_t)2 * heads * dim +
+                                  (size_t)h * vdim + col]);
+            vs[it] = v;
+        }
+        __syncthreads();
+        {   // A[i][j] = (q_i . k_j) g^(i - j) for j <= i: a 2 x 2 tile per thread
+            const int i0 = (tid >> 4) * 2, j0 = (tid & 15) * 2;
+            float a00 = 0.f, a01 = 0.f, a10 = 0.f, a11 = 0.f;
+            if (j0 <= i0 + 1) {
+                const float4* q0 = reinterpret_cast<const float4*>(qs + i0 * ld);
+                const float4* q1 = reinterpret_cast<const float4*>(qs + (i0 + 1) * ld);
+                const float4* k0 = reinterpret_cast<const float4*>(ks + j0 * ld);
+                const float4* k1 = reinterpret_cast<const float4*>(ks + (j0 + 1) * ld);
+#pragma unroll 4
+                for (int d = 0; d < dim / 4; ++d) {
+                    float4 x0 = q0[d], x1 = q1[d], y0 = k0[d], y1 = k1[d];
+                    a00 = fmaf(x0.x, y0.x, fmaf(x0.y, y0.y, fmaf(x0.z, y0.z, fmaf(x0.w, y0.w, a00))));
+                    a01 = fmaf(x0.x, y1.x, fmaf(x0.y, y1.y, fmaf(x0.z, y1.z, fmaf(x0.w, y1.w, a01))));
+                    a10 = fmaf(x1.x, y0.x, fmaf(x1.y, y0.y, fmaf(x1.z, y0.z, fmaf(x1.w, y0.w, a10))));
+                    a11 = fmaf(x1.x, y1.x, fmaf(x1.y, y1.y, fmaf(x1.z, y1.z, fmaf(x1.w, y1.w, a11))));
+                }
+            }
+            As[i0 * (C + 1) + j0] = j0 <= i0 ? a00 * pw[i0 - j0] : 0.f;
+            As[i0 * (C + 1) + j0 + 1] = j0 + 1 <= i0 ? a01 * pw[i0 - j0 - 1] : 0.f;
+            As[(i0 + 1) * (C + 1) + j0] = j0 <= i0 + 1 ? a10 * pw[i0 + 1 - j0] : 0.f;
+            As[(i0 + 1) * (C + 1) + j0 + 1] = j0 <= i0 ? a11 * pw[i0 - j0] : 0.f;
+        }
+        __syncthreads();
+        {   // outputs: rows 4 warp .. 4 warp + 3, column = lane
+            const int i0 = warp * 4;
+            float inter[4] = {0.f, 0.f, 0.f, 0.f}, intra[4] = {0.f, 0.f, 0.f, 0.f};
+            if (i0 < cnt) {
+#pragma unroll 2
+                for (int d = 0; d < dim; d += 4) {
+                    float s0 = Ss[d * 32 + lane], s1 = Ss[(d + 1) * 32 + lane];
+                    float s2 = Ss[(d + 2) * 32 + lane], s3 = Ss[(d + 3) * 32 + lane];
+#pragma unroll
+                    for (int r = 0; r < 4; ++r) {
+                        float4 x = *reinterpret_cast<const float4*>(qs + (i0 + r) * ld + d);
+                        inter[r] = fmaf(x.x, s0, fmaf(x.y, s1, fmaf(x.z, s2, fmaf(x.w, s3, inter[r]))));
+                    }
+                }
+                for (int j = 0; j <= i0 + 3; ++j) {  // (A is zero above its diagonal)
+                    float v = vs[j * 32 + lane];
+#pragma unroll
+                    for (int r = 0; r < 4; ++r) intra[r] = fmaf(As[(i0 + r) * (C + 1) + j], v, intra[r]);
+                }
+#pragma unroll
+                for (int r = 0; r < 4; ++r)
+                    if (live && i0 + r < cnt)
+                        o_raw[((size_t)(first + t0 + i0 + r) * heads + h) * vdim + col] =
+                            fmaf(pw[i0 + r + 1], inter[r], intra[r]);
+            }
+        }
+        __syncthreads();
+        {   // the state after the chunk: rows warp * DR .. + DR - 1, column = lane
+            const int d0 = warp * DR;
+            float acc[DR];
+#pragma unroll
+            for (int r = 0; r < DR; ++r) acc[r] = 0.f;
+            for (int j = 0; j < cnt; ++j) {
+                float v = pw[cnt - 1 - j] * vs[j * 32 + lane];
+#pragma unroll
+                for (int r4 = 0; r4 < DR4; ++r4) {
+                    float4 k = *reinterpret_cast<const float4*>(ks + j * ld + d0 + 4 * r4);
+                    acc[4 * r4] = fmaf(k.x, v, acc[4 * r4]);
+                    acc[4 * r4 + 1] = fmaf(k.y, v, acc[4 * r4 + 1]);
+                    acc[4 * r4 + 2] = fmaf(k.z, v, acc[4 * r4 + 2]);
+                    acc[4 * r4 + 3] = fmaf(k.w, v, acc[4 * r4 + 3]);
+                }
+            }
+#pragma unroll
+            for (int r = 0; r < DR; ++r) Ss[(d0 + r) * 32 + lane] = fmaf(pw[cnt], Ss[(d0 + r) * 32 + lane], acc[r]);
+        }
+    }
+    __syncthreads();
+    for (int d = warp; d < dim; d += 8)
+        if (live) S[(size_t)d * vdim + col] = Ss[d * 32 + lane];
+}
+
 // out[n, h, :] = o[n, h, :] / sqrt(mean(o[n, h, :]^2) + eps) * silu(g[n, h, :]); a warp
 // per (token, head); a row at position -1 is left alone
 template <typename T>
@@ -140,6 +295,35 @@ static int launch_retention(const void* qkvg, const float* freq, const float* de
                             float* o_raw, void* out, int n_tokens, int n_units, int heads, int dim,
                             int vdim, int rot_dims, float eps, cudaStream_t stream) {
     dim3 grid(n_units, heads, (vdim + 31) / 32);
+    if (seq_first_row && (dim == 32 || dim == 64 || dim == 128 || dim == 256)) {
+        // a prompt step: chunks of tokens (other key sizes walk the tokens one by one below)
+        constexpr int C = kRetChunk;
+        size_t chunk_smem = (2 * (size_t)C * (dim + 4) + (size_t)dim * 32 + C * (C + 1) + C * 32 + C + 1) *
+                            sizeof(float);
+        cudaError_t e = cudaSuccess;
+#define NNIS_RET_CHUNK(DR4) \
+        do { \
+            auto kernel = retention_chunk_kernel<T, DR4>; \
+            if (chunk_smem > 48 * 1024) \
+                e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)chunk_smem); \
+            if (e == cudaSuccess) \
+                kernel<<<grid, 256, chunk_smem, stream>>>((const T*)qkvg, freq, decay, state, seq_slots, \
+                                                          seq_first_row, seq_start, seq_count, o_raw, heads, \
+                                                          vdim, rot_dims); \
+        } while (0)
+        if (dim == 32) NNIS_RET_CHUNK(1);
+        else if (dim == 64) NNIS_RET_CHUNK(2);
+        else if (dim == 128) NNIS_RET_CHUNK(4);
+        else NNIS_RET_CHUNK(8);
+#undef NNIS_RET_CHUNK
+        if (e != cudaSuccess) return (int)e;
+        e = cudaGetLastError();
+        if (e != cudaSuccess) return (int)e;
+        long long gate_units = (long long)n_tokens * heads;
+        retention_gate_kernel<T><<<(unsigned)((gate_units + 7) / 8), 256, 0, stream>>>(
+            o_raw, (const T*)qkvg, token_pos, (T*)out, gate_units, heads, dim, vdim, eps);
+        NNIS_RETURN_LAUNCH();
+    }
     size_t smem = (2 * (size_t)dim + 256) * sizeof(float);
 #define NNIS_RET_CASE(R) \
     retention_scan_kernel<T, R><<<grid, 256, smem, stream>>>( \

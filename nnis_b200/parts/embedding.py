@@ -83,7 +83,8 @@ class LinearHead(Part):
         return 2.0 * self.vocab * self.width * wanted
 
     def forward(self, x: torch.Tensor, logits: torch.Tensor) -> None:
-        linear(x, self.weight, None, logits, STORE_F32)
+        # (few rows: the decode projection kernel where it takes the shape)
+        linear(x, self.weight, None, logits, STORE_F32, decode=True)
 
     def fuses_norm(self, norm, rows: int) -> bool:
         return (getattr(norm, "kind", None) == "rmsnorm" and self.dtype == torch.bfloat16

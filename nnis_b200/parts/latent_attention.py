@@ -138,12 +138,12 @@ class LatentAttention(Part):
         table = ctx.page_tables[cache.group]
         freq = self.position.frequencies()
         down = ws.get("latent_down", (n, self.q_rank + self.row), torch.float32)
-        linear(x, self.w_down, None, down, STORE_F32)
+        linear(x, self.w_down, None, down, STORE_F32, decode=ctx.decode)
         cq = ws.get("latent_cq", (n, self.q_rank), self.dtype)
         ops.latent_prep(down, self.norm_q, self.norm_kv, freq, ctx.token_pos, ctx.token_seq, table, cq,
                         cache.k, self.q_rank, self.kv_rank, self.rot, self.position.dims, self.eps)
         q = ws.get("latent_q", (n, H * (self.dim + self.rot)), self.dtype)
-        linear(cq, self.w_uq, None, q, STORE)
+        linear(cq, self.w_uq, None, q, STORE, decode=ctx.decode)
         q_lat = ws.get("latent_q_abs", (n, H * self.row), self.dtype)
         ops.batched_linear(q, self.dim + self.rot, self.w_ukt, q_lat, self.row)
         if self.rot:
@@ -170,7 +170,7 @@ class LatentAttention(Part):
                                  self.scale, splits, partial)
         attn = ws.get("attn", (n, H * self.vdim), self.dtype)
         ops.batched_linear(o_lat, self.kv_rank, self.w_uv, attn, self.vdim)
-        linear(attn, self.w_o, None, residual, ADD_F32, ws)
+        linear(attn, self.w_o, None, residual, ADD_F32, ws, decode=ctx.decode)
 
 
 MIXERS.register("latent_attention", LatentAttention)

@@ -18,12 +18,16 @@ STORE, STORE_F32, ADD_F32 = ops.STORE, ops.STORE_F32, ops.ADD_F32
 
 
 def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor,
-           mode: int, workspace=None) -> None:
+           mode: int, workspace=None, decode: bool = False) -> None:
     """``workspace``: the step's buffers (``engine.workspace.Workspace``); with it the adding
     tensor-core product may cut a long K among several CTAs per tile (few rows, few tiles),
-    which needs scratch for their partial sums."""
+    which needs scratch for their partial sums.  ``decode``: the step brings one token per
+    sequence; a bfloat16 product of few rows then runs as a decode projection kernel (weights
+    by bulk copies ahead of the wait for the kernel before) where that kernel takes the shape."""
     m, (n, k) = x.shape[0], weight.shape
-    if x.dtype == torch.bfloat16 and ops.gemm_tc_takes(m, n, k):
+    if decode and x.dtype == torch.bfloat16 and ops.gemv_pays(m, n, k, mode, x.device):
+        ops.gemv_bf16(weight, bias, out, mode, x=x)  # (STORE, STORE_F32, ADD_F32 are its epilogues' codes)
+    elif x.dtype == torch.bfloat16 and ops.gemm_tc_takes(m, n, k):
         scratch = tickets = None
         if mode == ADD_F32 and workspace is not None and ops.GEMM_SPLIT_K:
             splits, floats, tiles = ops.gemm_tc_splits(m, n, k, x.device)

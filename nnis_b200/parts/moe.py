@@ -10,7 +10,9 @@ the shared expert's up-projection, and since it scales the whole output it is
 applied to the activation, before the down-projection adds into the residual.
 
 The experts' matrices are stacked ([experts, ff, width] and [experts, width, ff]) so
-that one kernel serves all of them from the router's ids.
+that one kernel serves all of them from the router's ids.  Steps of few tokens run a
+product per (token, chosen expert); prompt steps in bfloat16 sort the pairs by expert and
+run two grouped products on the tensor cores.
 
 params: hidden_size, experts, top, ff, shared_ff (0: no shared expert), activation
 ("relu2"), names {router, router_bias, expert (a format with {e}), up, down,
@@ -29,6 +31,8 @@ from .linear import ADD_F32, STORE_F32, linear
 
 
 class MoEFeedForward(Part):
+    GROUPED_FROM = 32  # tokens of a prompt step from which the pairs are sorted by expert
+
     def __init__(self, params, prefix, dtype, device):
         super().__init__(params, prefix, dtype, device)
         self.hidden = int(params["hidden_size"])
@@ -68,8 +72,12 @@ class MoEFeedForward(Part):
         self.w_up = torch.stack([tensors[self._expert(e, "up")] for e in range(self.experts)]).contiguous()
         self.w_down = torch.stack([tensors[self._expert(e, "down")] for e in range(self.experts)]).contiguous()
         if self.shared_ff:
-            self.w_shared_up = torch.cat([tensors[self.tensor_name(self.names["shared_up"])],
-                                          tensors[self.tensor_name(self.names["shared_gate"])]], 0).contiguous()
+            up = tensors[self.tensor_name(self.names["shared_up"])]
+            gate = tensors[self.tensor_name(self.names["shared_gate"])]
+            # the gate's row after the up-projection's, then zero rows up to a multiple of eight
+            # (the decode projection kernels take output rows in eights)
+            pad = up.new_zeros((-(self.shared_ff + 1) % 8, self.hidden))
+            self.w_shared_up = torch.cat([up, gate, pad], 0).contiguous()
             self.w_shared_down = tensors[self.tensor_name(self.names["shared_down"])]
 
     def parameter_bytes(self) -> int:
@@ -90,14 +98,25 @@ class MoEFeedForward(Part):
         ids = ws.get("moe_ids", (n, self.top), torch.int32)
         weights = ws.get("moe_weights", (n, self.top), torch.float32)
         ops.moe_route(x, self.w_router, self.b_router, ctx.token_pos, ids, weights, self.top)
-        act = ws.get("moe_act", (n, self.top, self.ff), self.dtype)
-        ops.moe_experts(x, self.w_up, self.w_down, ids, weights, ctx.token_pos, act, residual, self.top)
+        if self.dtype == torch.bfloat16 and not ctx.decode and n >= self.GROUPED_FROM \
+                and ops.moe_grouped_takes(self.hidden, self.ff, self.experts):
+            # many tokens: pairs sorted by expert, grouped products on the tensor cores
+            tiles = ops.moe_grouped_tiles(n * self.top, self.experts)
+            ops.moe_grouped(x, self.w_up, self.w_down, ids, weights,
+                            ws.get("moe_perm", (tiles * 64,), torch.int32),
+                            ws.get("moe_place", (n * self.top,), torch.int32),
+                            ws.get("moe_tile_expert", (tiles,), torch.int32),
+                            ws.get("moe_act_sorted", (tiles * 64, self.ff), self.dtype),
+                            ws.get("moe_y_sorted", (tiles * 64, self.hidden), torch.float32), residual, self.top)
+        else:
+            act = ws.get("moe_act", (n, self.top, self.ff), self.dtype)
+            ops.moe_experts(x, self.w_up, self.w_down, ids, weights, ctx.token_pos, act, residual, self.top)
         if self.shared_ff:
-            up = ws.get("moe_shared_up", (n, self.shared_ff + 1), torch.float32)
-            linear(x, self.w_shared_up, None, up, STORE_F32)
+            up = ws.get("moe_shared_up", (n, self.w_shared_up.shape[0]), torch.float32)
+            linear(x, self.w_shared_up, None, up, STORE_F32, decode=ctx.decode)
             shared_act = ws.get("moe_shared_act", (n, self.shared_ff), self.dtype)
-            ops.relu2_gate(up, shared_act, True)
-            linear(shared_act, self.w_shared_down, None, residual, ADD_F32, ws)
+            ops.relu2_gate(up, shared_act)
+            linear(shared_act, self.w_shared_down, None, residual, ADD_F32, ws, decode=ctx.decode)
 
 
 FEED_FORWARDS.register("moe", MoEFeedForward)

@@ -84,13 +84,13 @@ class Retention(Part):
         n = residual.shape[0]
         H, ws = self.heads, ctx.workspace
         qkvg = ws.get("retention_in", (n, 2 * H * (self.dim + self.vdim)), self.dtype)
-        linear(x, self.w_in, None, qkvg, STORE)
+        linear(x, self.w_in, None, qkvg, STORE, decode=ctx.decode)
         o_raw = ws.get("retention_o", (n, H * self.vdim), torch.float32)
         gated = ws.get("retention_gated", (n, H * self.vdim), self.dtype)
         ops.retention(qkvg, self.position.frequencies(), self._decay, cache.state, ctx.token_pos,
                       ctx.token_seq, ctx.seq_slots, ctx.seq_first_row, ctx.seq_start, ctx.seq_count,
                       o_raw, gated, H, self.dim, self.vdim, self.position.dims, self.eps)
-        linear(gated, self.w_o, None, residual, ADD_F32, ws)
+        linear(gated, self.w_o, None, residual, ADD_F32, ws, decode=ctx.decode)
 
 
 MIXERS.register("retention", Retention)
