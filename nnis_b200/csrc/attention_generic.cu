@@ -141,7 +141,7 @@ static int launch_attention(const void* q, int q_stride, const void* k_cache, co
     if (e != cudaSuccess) return (int)e;
     if (n_splits > 1) {
         size_t rows = (size_t)n_tokens * nq;
-        attn_merge_kernel<T><<<(unsigned)((rows + 3) / 4), 128, 0, stream>>>(partial, (T*)out, rows,
+        attn_merge_kernel<T><<<(unsigned)rows, 128, 0, stream>>>(partial, (T*)out, rows,
                                                                              d, n_splits);
     }
     NNIS_RETURN_LAUNCH();
@@ -153,7 +153,7 @@ static int launch_attention(const void* q, int q_stride, const void* k_cache, co
 extern "C" int nnis_attention_merge_bf16(const float* partial, void* out, long long n_rows, int d,
                                          int n_splits, cudaStream_t stream) {
     if (n_splits > 64) return NNIS_ERR_UNSUPPORTED;
-    nnis::attn_merge_kernel<nnis::bf16><<<(unsigned)((n_rows + 3) / 4), 128, 0, stream>>>(
+    nnis::attn_merge_kernel<nnis::bf16><<<(unsigned)n_rows, 128, 0, stream>>>(
         partial, (nnis::bf16*)out, (size_t)n_rows, d, n_splits);
     NNIS_RETURN_LAUNCH();
 }

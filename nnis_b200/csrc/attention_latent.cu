@@ -176,7 +176,7 @@ static int launch_latent(const void* q, const void* cache, const int* token_pos,
     if (e != cudaSuccess) return (int)e;
     if (n_splits > 1) {
         size_t rows = (size_t)n_tokens * heads;
-        attn_merge_kernel<T><<<(unsigned)((rows + 3) / 4), 128, 0, stream>>>(partial, (T*)out, rows, dv,
+        attn_merge_kernel<T><<<(unsigned)rows, 128, 0, stream>>>(partial, (T*)out, rows, dv,
                                                                              n_splits);
     }
     NNIS_RETURN_LAUNCH();

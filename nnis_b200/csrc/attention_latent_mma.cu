@@ -1,12 +1,13 @@
 // Latent attention on the tensor cores (bfloat16): all heads of a token share the
 // cached rows [c | kr], so the (token, head) pairs of a sequence are stacked into the
-// rows of one matrix [tokens * heads, dk] and a CTA of four warps owns 64 consecutive
-// stacked rows: with 8 heads that is 8 query tokens, with 64 heads one.  A prompt, a
+// rows of one matrix [tokens * heads, dk] and a CTA owns 64 consecutive stacked rows
+// (eight warps: two groups of four, each group a run of output values): with 8 heads
+// that is 8 query tokens, with 64 heads one.  A prompt, a
 // later chunk and a single decoded token are the same case (one token gives `heads`
 // rows).  The CTA walks the sequence's pages (64 positions) up to its last query; a
 // page comes into swizzled shared memory once, by 16-byte cp.async copies, and serves
 // both products: scores S = Q K^T over all dk values of the rows, and O += P V over
-// their first dv values, of which a CTA takes a run of up to 128 (blockIdx.y).  The
+// their first dv values, of which a warp group takes a run of up to 128.  The
 // online softmax between the products is float32 in registers.  Rows in shared memory
 // are padded to a multiple of 64 values (zeros) so that the XOR swizzle stays inside a row.
 //
@@ -29,7 +30,7 @@ __device__ __forceinline__ int swz_rt(int row, int chunk, int width) {
 }
 
 template <int STAGES>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(256)
 latent_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ cache,
                   const int* __restrict__ tiles, const int* __restrict__ seq_first_row,
                   const int* __restrict__ seq_start, const int* __restrict__ seq_count,
@@ -41,7 +42,9 @@ latent_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ cache,
     extern __shared__ __align__(128) unsigned char smem_raw[];
     bf16* q_s = reinterpret_cast<bf16*>(smem_raw);       // [64, dkp] swizzled
     bf16* k_s = q_s + (size_t)kLatRows * dkp;            // stages x [64, dkp]
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, tid = threadIdx.x;
+    // eight warps: warps 0-3 and 4-7 own the same 64 rows and two runs of output values
+    const int lane = threadIdx.x & 31, warp = (threadIdx.x >> 5) & 3, group = threadIdx.x >> 7;
+    const int tid = threadIdx.x;
     const int CH = dk >> 3, CHP = dkp >> 3;
     int seq, r0, count, start, first;
     if (tiles) {
@@ -61,8 +64,9 @@ latent_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ cache,
     const int total = count * heads;                 // stacked rows of this sequence's step
     const int rows = min(kLatRows, total - r0);      // valid rows of the tile
     const size_t row_base = (size_t)first * heads + r0;
-    const int c0 = blockIdx.y * (kLatChunk / 8);     // first 16-byte chunk of this CTA's values
-    const int dv_here = min(kLatChunk, dv - blockIdx.y * kLatChunk);
+    const int run = blockIdx.y * 2 + group;          // this warp group's run of output values
+    const int c0 = run * (kLatChunk / 8);            // its first 16-byte chunk
+    const int dv_here = min(kLatChunk, dv - run * kLatChunk);  // (<= 0: the group only helps to copy)
     const int split = blockIdx.z;
     if (rows <= 0) {
         return;  // (a padding row: the merge and the projections after it read nothing of it)
@@ -78,7 +82,7 @@ latent_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ cache,
     // the padding columns of every buffer are zero and stay zero
     if (CHP > CH) {
         const int padc = CHP - CH;
-        for (int c = tid; c < (1 + STAGES) * kLatRows * padc; c += 128) {
+        for (int c = tid; c < (1 + STAGES) * kLatRows * padc; c += 256) {
             int buf = c / (kLatRows * padc), rem = c - buf * kLatRows * padc;
             int row = rem / padc, chunk = CH + rem % padc;
             *reinterpret_cast<uint4*>(q_s + (size_t)buf * tile_elems + swz_rt(row, chunk, dkp)) =
@@ -90,7 +94,7 @@ latent_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ cache,
             int page = table[first_page + it];
             const bf16* src = cache + (size_t)page * kLatPage * dk;
             bf16* dst = k_s + (size_t)(it % STAGES) * tile_elems;
-            for (int c = tid; c < kLatPage * CH; c += 128) {
+            for (int c = tid; c < kLatPage * CH; c += 256) {
                 int row = c / CH, chunk = c - row * CH;
                 cp_async16(dst + swz_rt(row, chunk, dkp), src + (size_t)c * 8);
             }
@@ -98,7 +102,7 @@ latent_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ cache,
         cp_async_commit();
     };
     for (int it = 0; it < STAGES - 1; ++it) load_page(it);
-    for (int c = tid; c < kLatRows * CH; c += 128) {
+    for (int c = tid; c < kLatRows * CH; c += 256) {
         int row = c / CH, chunk = c - row * CH;
         uint4 v = make_uint4(0, 0, 0, 0);
         if (row < rows) v = *reinterpret_cast<const uint4*>(q + (row_base + row) * dk + chunk * 8);
@@ -126,7 +130,7 @@ latent_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ cache,
         load_page(it + STAGES - 1);
         const bf16* kt = k_s + (size_t)(it % STAGES) * tile_elems;
         const int t0 = (first_page + it) * kLatPage;
-        if (t0 > warp_last_pos) continue;  // none of this warp's rows sees the page
+        if (t0 > warp_last_pos || dv_here <= 0) continue;  // none of this warp's rows sees the page
 
         float s[8][4];
 #pragma unroll
@@ -209,7 +213,7 @@ latent_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ cache,
         for (int jn = 0; jn < NT; ++jn) {
             int col = jn * 8 + c_lo;
             if (col < dv_here) {
-                int gc = blockIdx.y * kLatChunk + col;
+                int gc = run * kLatChunk + col;
                 if (ra < rows)
                     *reinterpret_cast<uint32_t*>(out + (row_base + ra) * dv + gc) =
                         pack_bf16(o[jn][0] * inv_a, o[jn][1] * inv_a);
@@ -226,7 +230,7 @@ latent_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ cache,
             int r = h ? rb : ra;
             if (r >= rows) continue;
             float* rec = partial + ((row_base + r) * n_splits + split) * (size_t)(dv + 2);
-            if (blockIdx.y == 0 && (lane & 3) == 0) {
+            if (run == 0 && (lane & 3) == 0) {
                 rec[0] = l_run[h] > 0.f ? m_run[h] * ln2 : 0.f;
                 rec[1] = l_run[h];
             }
@@ -234,7 +238,7 @@ latent_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ cache,
             for (int jn = 0; jn < NT; ++jn) {
                 int col = jn * 8 + c_lo;
                 if (col < dv_here) {
-                    int gc = blockIdx.y * kLatChunk + col;
+                    int gc = run * kLatChunk + col;
                     rec[2 + gc] = o[jn][h * 2];
                     rec[2 + gc + 1] = o[jn][h * 2 + 1];
                 }
@@ -282,22 +286,22 @@ NNIS_API int nnis_attention_latent_mma(const void* q, const void* cache, const i
     const int tiles_per_token = (heads + kLatRows - 1) / kLatRows;
     const int chunks = (dv + kLatChunk - 1) / kLatChunk;
     if (chunks > 65535 || n_splits > 64) return NNIS_ERR_UNSUPPORTED;
-    dim3 grid(tiles ? n_tiles : n_tokens * tiles_per_token, chunks, n_splits);
-    const int stages = latent_mma_smem(dk, 3) <= 100 * 1024 ? 3 : 2;
+    dim3 grid(tiles ? n_tiles : n_tokens * tiles_per_token, (chunks + 1) / 2, n_splits);
+    const int stages = latent_mma_smem(dk, 3) <= 200 * 1024 ? 3 : 2;
     const size_t smem = latent_mma_smem(dk, stages);
     auto kernel = stages == 3 ? latent_mma_kernel<3> : latent_mma_kernel<2>;
     if (smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
     }
-    kernel<<<grid, 128, smem, stream>>>((const bf16*)q, (const bf16*)cache, tiles, seq_first_row, seq_start,
+    kernel<<<grid, 256, smem, stream>>>((const bf16*)q, (const bf16*)cache, tiles, seq_first_row, seq_start,
                                         seq_count, token_pos, token_seq, page_table, table_cols, (bf16*)out,
                                         partial, heads, dk, dv, dkp, tiles_per_token, scale, n_splits);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return (int)e;
     if (n_splits > 1) {
         size_t rows = (size_t)n_tokens * heads;
-        attn_merge_kernel<bf16><<<(unsigned)((rows + 3) / 4), 128, 0, stream>>>(partial, (bf16*)out, rows, dv,
+        attn_merge_kernel<bf16><<<(unsigned)rows, 128, 0, stream>>>(partial, (bf16*)out, rows, dv,
                                                                                 n_splits);
     }
     NNIS_RETURN_LAUNCH();

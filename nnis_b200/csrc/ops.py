@@ -1053,12 +1053,23 @@ def retention(qkvg: torch.Tensor, freq: torch.Tensor, decay: torch.Tensor, state
               token_pos: torch.Tensor, token_seq: torch.Tensor, seq_slots: torch.Tensor,
               seq_first_row: Optional[torch.Tensor], seq_start: Optional[torch.Tensor],
               seq_count: Optional[torch.Tensor], o_raw: torch.Tensor, out: torch.Tensor, heads: int,
-              dim: int, vdim: int, rot_dims: int, eps: float) -> None:
+              dim: int, vdim: int, rot_dims: int, eps: float, segments: Optional[torch.Tensor] = None,
+              seq_first_segment: Optional[torch.Tensor] = None, seg_state: Optional[torch.Tensor] = None,
+              seg_len: int = 0) -> None:
     """Retention of packed rows [q | k | v | g] from and into the per-slot state
     [slots, heads, dim, vdim] (float32); out [n, heads * vdim] = o / rms(o) * silu(g).
-    Without ``seq_first_row`` every row is one token of a sequence of its own."""
+    Without ``seq_first_row`` every row is one token of a sequence of its own.  With
+    ``segments`` (``retention_segments``) a prompt step's sequences are cut into runs of
+    ``seg_len`` tokens that are worked side by side (``retention_takes_segments``)."""
     _cuda(qkvg, freq, decay, state, token_pos, token_seq, seq_slots, seq_first_row, seq_start, seq_count,
-          o_raw, out)
+          o_raw, out, segments, seq_first_segment, seg_state)
+    n_segments = 0
+    if segments is not None:
+        n_segments = segments.shape[0]
+        _need(retention_takes_segments(dim) and seq_first_row is not None and seq_first_segment is not None
+              and seg_state is not None and seg_state.dtype == torch.float32
+              and seg_state.numel() >= n_segments * heads * dim * vdim and seg_len > 0,
+              "retention: segments need a prompt step, their tables and scratch")
     n = out.shape[0]
     _need(qkvg.shape[0] >= n and qkvg.shape[1] == 2 * heads * (dim + vdim) and qkvg.dtype == out.dtype,
           "retention: rows [n, 2 heads (dim + vdim)]")
@@ -1071,9 +1082,29 @@ def retention(qkvg: torch.Tensor, freq: torch.Tensor, decay: torch.Tensor, state
     units = seq_first_row.numel() if seq_first_row is not None else n
     _check(_lib().nnis_retention(_ptr(qkvg), _ptr(freq), _ptr(decay), _ptr(state), _ptr(token_pos),
                                  _ptr(token_seq), _ptr(seq_slots), _ptr(seq_first_row), _ptr(seq_start),
-                                 _ptr(seq_count), _ptr(o_raw), _ptr(out), n, units, heads, dim, vdim,
+                                 _ptr(seq_count), _ptr(segments), n_segments, _ptr(seq_first_segment), seg_len,
+                                 _ptr(seg_state), _ptr(o_raw), _ptr(out), n, units, heads, dim, vdim,
                                  rot_dims, ctypes.c_float(eps), code_of(out.dtype), _stream()),
-           "retention", 2)
+           "retention", 4 if segments is not None else 2)
+
+
+RETENTION_SEGMENT = int(os.environ.get("NNIS_RETENTION_SEGMENT", "256"))  # tokens of a run; 0: no runs
+
+
+def retention_takes_segments(dim: int) -> bool:
+    """Whether prompts of these key sizes can be cut into runs worked side by side."""
+    return RETENTION_SEGMENT > 0 and RETENTION_SEGMENT % 32 == 0 and dim in (32, 64, 128, 256)
+
+
+def retention_segments(counts, seg_len: int):
+    """(segments [n, 2] = (sequence, first token of the run), first segment of every
+    sequence [sequences + 1]) for a prompt step whose sequences bring ``counts`` tokens."""
+    import numpy as np
+    segments, first = [], [0]
+    for i, c in enumerate(counts):
+        segments += [(i, t) for t in range(0, int(c), seg_len)]
+        first.append(len(segments))
+    return np.asarray(segments, dtype=np.int32).reshape(-1, 2), np.asarray(first, dtype=np.int32)
 
 
 def moe_route(h: torch.Tensor, w_router: torch.Tensor, b_router: Optional[torch.Tensor],

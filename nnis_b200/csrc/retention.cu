@@ -122,6 +122,7 @@ retention_chunk_kernel(const T* __restrict__ qkvg, const float* __restrict__ fre
                        const float* __restrict__ decay, float* __restrict__ state,
                        const int* __restrict__ seq_slots, const int* __restrict__ seq_first_row,
                        const int* __restrict__ seq_start, const int* __restrict__ seq_count,
+                       const int* __restrict__ segments, int seg_len, float* __restrict__ seg_state,
                        float* __restrict__ o_raw, int heads, int vdim, int rot_dims) {
     constexpr int C = kRetChunk, dim = 32 * DR4, ld = dim + 4, DR = 4 * DR4;
     extern __shared__ __align__(16) float smem[];
@@ -131,16 +132,23 @@ retention_chunk_kernel(const T* __restrict__ qkvg, const float* __restrict__ fre
     float* As = Ss + dim * 32;         // [C][C + 1]
     float* vs = As + C * (C + 1);      // [C][32]
     float* pw = vs + C * 32;           // [C + 1]: g^n
-    const int unit = blockIdx.x, h = blockIdx.y;
+    const int h = blockIdx.y;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, tid = threadIdx.x;
     const int col = blockIdx.z * 32 + lane;
-    const int first = seq_first_row[unit], start = seq_start[unit], count = seq_count[unit];
+    // a unit is a sequence, from and into its state; or, with `segments`, a run of seg_len
+    // tokens of a sequence from a zero state into a state of its own (retention_carry adds
+    // what the tokens before the run contribute)
+    const int unit = segments ? segments[2 * blockIdx.x] : (int)blockIdx.x;
+    const int begin = segments ? segments[2 * blockIdx.x + 1] : 0;
+    const int first = seq_first_row[unit] + begin, start = seq_start[unit] + begin;
+    const int count = segments ? min(seg_len, seq_count[unit] - begin) : seq_count[unit];
     if (count <= 0) return;
     const bool live = col < vdim;
     const float g = decay[h];
     const float k_scale = 1.0f / sqrtf((float)dim);
-    float* S = state + (((size_t)seq_slots[unit] * heads + h) * dim) * vdim;
-    for (int d = warp; d < dim; d += 8) Ss[d * 32 + lane] = live ? S[(size_t)d * vdim + col] : 0.f;
+    float* S = segments ? seg_state + (((size_t)blockIdx.x * heads + h) * dim) * vdim
+                        : state + (((size_t)seq_slots[unit] * heads + h) * dim) * vdim;
+    for (int d = warp; d < dim; d += 8) Ss[d * 32 + lane] = live && !segments ? S[(size_t)d * vdim + col] : 0.f;
     for (int it = tid; it < 2 * C * ld; it += 256) qs[it] = 0.f;  // (rows beyond a short chunk)
     if (tid == 0) {
         float p = 1.f;
@@ -258,6 +266,107 @@ retention_chunk_kernel(const T* __restrict__ qkvg, const float* __restrict__ fre
         if (live) S[(size_t)d * vdim + col] = Ss[d * 32 + lane];
 }
 
+// Long prompts run as runs of seg_len tokens side by side (retention_chunk with `segments`),
+// each from a zero state.  This kernel then walks a sequence's runs in order, per element of
+// the state: the state before a run replaces the run's own in `seg_state`, and the state
+// after the last run goes to the sequence's slot.  S_before(r + 1) = g^len(r) S_before(r) + U(r).
+__global__ void __launch_bounds__(256)
+retention_prefix_kernel(float* __restrict__ seg_state, float* __restrict__ state,
+                        const float* __restrict__ decay, const int* __restrict__ seq_slots,
+                        const int* __restrict__ seq_count, const int* __restrict__ seq_first_segment,
+                        int seg_len, int heads, int per_head) {
+    const int b = blockIdx.x, h = blockIdx.y;
+    const int e = blockIdx.z * 256 + threadIdx.x;
+    if (e >= per_head) return;
+    const int s0 = seq_first_segment[b], s1 = seq_first_segment[b + 1], count = seq_count[b];
+    const float g = decay[h];
+    float* cell = state + ((size_t)seq_slots[b] * heads + h) * per_head + e;
+    float run = *cell;
+    for (int s = s0; s < s1; ++s) {
+        int len = min(seg_len, count - (s - s0) * seg_len);
+        float p = 1.f;
+        for (int n = 0; n < len; ++n) p *= g;
+        float* u = seg_state + ((size_t)s * heads + h) * per_head + e;
+        float after = fmaf(p, run, *u);
+        *u = run;
+        run = after;
+    }
+    *cell = run;
+}
+
+// ... and this one adds to every token of a run what the state before the run gives it:
+// o_i += g^(i + 1) S_before^T q_i, i counted within the run.
+template <typename T, int DR4>
+__global__ void __launch_bounds__(256)
+retention_carry_kernel(const T* __restrict__ qkvg, const float* __restrict__ freq,
+                       const float* __restrict__ decay, const float* __restrict__ seg_state,
+                       const int* __restrict__ seq_first_row, const int* __restrict__ seq_start,
+                       const int* __restrict__ seq_count, const int* __restrict__ segments, int seg_len,
+                       float* __restrict__ o_raw, int heads, int vdim, int rot_dims) {
+    constexpr int C = kRetChunk, dim = 32 * DR4, ld = dim + 4;
+    extern __shared__ __align__(16) float smem[];
+    float* qs = smem;             // [C][dim + 4]
+    float* Ss = qs + C * ld;      // [dim][32]
+    float* pw = Ss + dim * 32;    // [seg_len + 1]
+    const int h = blockIdx.y, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, tid = threadIdx.x;
+    const int col = blockIdx.z * 32 + lane;
+    const int unit = segments[2 * blockIdx.x], begin = segments[2 * blockIdx.x + 1];
+    const int first = seq_first_row[unit] + begin, start = seq_start[unit] + begin;
+    const int count = min(seg_len, seq_count[unit] - begin);
+    if (count <= 0 || (begin == 0 && seq_start[unit] == 0)) return;  // (nothing before a sequence's start)
+    const bool live = col < vdim;
+    const float* S = seg_state + (((size_t)blockIdx.x * heads + h) * dim) * vdim;
+    for (int d = warp; d < dim; d += 8) Ss[d * 32 + lane] = live ? S[(size_t)d * vdim + col] : 0.f;
+    for (int it = tid; it < C * ld; it += 256) qs[it] = 0.f;
+    if (tid == 0) {
+        float p = 1.f, g = decay[h];
+        for (int n = 0; n <= seg_len; ++n) {
+            pw[n] = p;
+            p *= g;
+        }
+    }
+    const size_t row_len = (size_t)2 * heads * dim + (size_t)2 * heads * vdim;
+    const int half = rot_dims >> 1, per_tok = dim - half;
+    for (int t0 = 0; t0 < count; t0 += C) {
+        const int cnt = min(C, count - t0);
+        __syncthreads();
+        for (int it = tid; it < cnt * per_tok; it += 256) {
+            int i = it / per_tok, j = it - i * per_tok;
+            const T* qh = qkvg + (size_t)(first + t0 + i) * row_len + (size_t)h * dim;
+            if (j < half) {
+                float ang = (float)(start + t0 + i) * freq[j];
+                float c = cosf(ang), sn = sinf(ang);
+                float u = to_float(qh[j]), v = to_float(qh[j + half]);
+                qs[i * ld + j] = u * c - v * sn;
+                qs[i * ld + j + half] = v * c + u * sn;
+            } else {
+                qs[i * ld + j + half] = to_float(qh[j + half]);
+            }
+        }
+        __syncthreads();
+        const int i0 = warp * 4;
+        if (i0 < cnt) {
+            float inter[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 2
+            for (int d = 0; d < dim; d += 4) {
+                float s0 = Ss[d * 32 + lane], s1 = Ss[(d + 1) * 32 + lane];
+                float s2 = Ss[(d + 2) * 32 + lane], s3 = Ss[(d + 3) * 32 + lane];
+#pragma unroll
+                for (int r = 0; r < 4; ++r) {
+                    float4 x = *reinterpret_cast<const float4*>(qs + (i0 + r) * ld + d);
+                    inter[r] = fmaf(x.x, s0, fmaf(x.y, s1, fmaf(x.z, s2, fmaf(x.w, s3, inter[r]))));
+                }
+            }
+#pragma unroll
+            for (int r = 0; r < 4; ++r)
+                if (live && i0 + r < cnt) {
+                    float* o = o_raw + ((size_t)(first + t0 + i0 + r) * heads + h) * vdim + col;
+                    *o = fmaf(pw[t0 + i0 + r + 1], inter[r], *o);
+                }
+        }
+    }
+}
+
 // out[n, h, :] = o[n, h, :] / sqrt(mean(o[n, h, :]^2) + eps) * silu(g[n, h, :]); a warp
 // per (token, head); a row at position -1 is left alone
 template <typename T>
@@ -292,7 +401,8 @@ template <typename T>
 static int launch_retention(const void* qkvg, const float* freq, const float* decay, float* state,
                             const int* token_pos, const int* token_seq, const int* seq_slots,
                             const int* seq_first_row, const int* seq_start, const int* seq_count,
-                            float* o_raw, void* out, int n_tokens, int n_units, int heads, int dim,
+                            const int* segments, int n_segments, const int* seq_first_segment, int seg_len,
+                            float* seg_state, float* o_raw, void* out, int n_tokens, int n_units, int heads, int dim,
                             int vdim, int rot_dims, float eps, cudaStream_t stream) {
     dim3 grid(n_units, heads, (vdim + 31) / 32);
     if (seq_first_row && (dim == 32 || dim == 64 || dim == 128 || dim == 256)) {
@@ -300,6 +410,8 @@ static int launch_retention(const void* qkvg, const float* freq, const float* de
         constexpr int C = kRetChunk;
         size_t chunk_smem = (2 * (size_t)C * (dim + 4) + (size_t)dim * 32 + C * (C + 1) + C * 32 + C + 1) *
                             sizeof(float);
+        size_t carry_smem = ((size_t)C * (dim + 4) + (size_t)dim * 32 + seg_len + 1) * sizeof(float);
+        dim3 chunk_grid(segments ? n_segments : n_units, heads, (vdim + 31) / 32);
         cudaError_t e = cudaSuccess;
 #define NNIS_RET_CHUNK(DR4) \
         do { \
@@ -307,9 +419,20 @@ static int launch_retention(const void* qkvg, const float* freq, const float* de
             if (chunk_smem > 48 * 1024) \
                 e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)chunk_smem); \
             if (e == cudaSuccess) \
-                kernel<<<grid, 256, chunk_smem, stream>>>((const T*)qkvg, freq, decay, state, seq_slots, \
-                                                          seq_first_row, seq_start, seq_count, o_raw, heads, \
-                                                          vdim, rot_dims); \
+                kernel<<<chunk_grid, 256, chunk_smem, stream>>>((const T*)qkvg, freq, decay, state, seq_slots, \
+                                                                seq_first_row, seq_start, seq_count, segments, \
+                                                                seg_len, seg_state, o_raw, heads, vdim, rot_dims); \
+            if (e == cudaSuccess && segments) { \
+                retention_prefix_kernel<<<dim3(n_units, heads, (dim * vdim + 255) / 256), 256, 0, stream>>>( \
+                    seg_state, state, decay, seq_slots, seq_count, seq_first_segment, seg_len, heads, dim * vdim); \
+                auto carry = retention_carry_kernel<T, DR4>; \
+                if (carry_smem > 48 * 1024) \
+                    e = cudaFuncSetAttribute(carry, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)carry_smem); \
+                if (e == cudaSuccess) \
+                    carry<<<chunk_grid, 256, carry_smem, stream>>>((const T*)qkvg, freq, decay, seg_state, \
+                                                                   seq_first_row, seq_start, seq_count, segments, \
+                                                                   seg_len, o_raw, heads, vdim, rot_dims); \
+            } \
         } while (0)
         if (dim == 32) NNIS_RET_CHUNK(1);
         else if (dim == 64) NNIS_RET_CHUNK(2);
@@ -349,24 +472,35 @@ using namespace nnis;
 // `seq_first_row` null: every row is a sequence of its own bringing one token
 // (`n_units` = n_tokens); else `n_units` sequences with their first row, first
 // position and token count.  `o_raw`: float32 scratch [n_tokens, heads * vdim].
+// `segments` (optional, prompt steps): int32 [n_segments, 2] = (sequence, first token of
+// the run among the sequence's tokens of this step), runs of `seg_len` tokens in the order
+// of the sequences, with `seq_first_segment` [n_units + 1] and `seg_state` float32
+// [n_segments, heads, dim, vdim]: the runs are worked side by side.
 NNIS_API int nnis_retention(const void* qkvg, const float* freq, const float* decay, float* state,
                             const int* token_pos, const int* token_seq, const int* seq_slots,
                             const int* seq_first_row, const int* seq_start, const int* seq_count,
-                            float* o_raw, void* out, int n_tokens, int n_units, int heads, int dim,
+                            const int* segments, int n_segments, const int* seq_first_segment, int seg_len,
+                            float* seg_state, float* o_raw, void* out, int n_tokens, int n_units, int heads, int dim,
                             int vdim, int rot_dims, float eps, int dtype, cudaStream_t stream) {
     if (n_tokens <= 0 || n_units <= 0 || heads <= 0 || dim <= 0 || vdim <= 0 || rot_dims < 0 ||
         (rot_dims & 1) || rot_dims > dim || !(eps > 0.f) || !qkvg || !freq || !decay || !state ||
         !token_pos || !token_seq || !seq_slots || !o_raw || !out)
         return NNIS_ERR_ARGUMENT;
     if (seq_first_row && (!seq_start || !seq_count)) return NNIS_ERR_ARGUMENT;
+    // runs side by side: only for prompt steps of key sizes the chunk kernel takes
+    if (segments && (!seq_first_row || n_segments <= 0 || !seq_first_segment || !seg_state || seg_len <= 0 ||
+                     seg_len % 32 || seg_len > 4096 || !(dim == 32 || dim == 64 || dim == 128 || dim == 256)))
+        return NNIS_ERR_ARGUMENT;
     if (dim > 256 || heads > 65535 || (vdim + 31) / 32 > 65535) return NNIS_ERR_UNSUPPORTED;
     if (dtype == NNIS_DTYPE_F32)
         return launch_retention<float>(qkvg, freq, decay, state, token_pos, token_seq, seq_slots,
-                                       seq_first_row, seq_start, seq_count, o_raw, out, n_tokens,
+                                       seq_first_row, seq_start, seq_count, segments, n_segments,
+                                       seq_first_segment, seg_len, seg_state, o_raw, out, n_tokens,
                                        n_units, heads, dim, vdim, rot_dims, eps, stream);
     if (dtype == NNIS_DTYPE_BF16)
         return launch_retention<bf16>(qkvg, freq, decay, state, token_pos, token_seq, seq_slots,
-                                      seq_first_row, seq_start, seq_count, o_raw, out, n_tokens,
+                                      seq_first_row, seq_start, seq_count, segments, n_segments,
+                                      seq_first_segment, seg_len, seg_state, o_raw, out, n_tokens,
                                       n_units, heads, dim, vdim, rot_dims, eps, stream);
     return NNIS_ERR_UNSUPPORTED;
 }

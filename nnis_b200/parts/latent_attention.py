@@ -126,7 +126,7 @@ class LatentAttention(Part):
     def _decode_splits(self, ctx, n: int) -> int:
         """Slices of the key range in a step of single tokens: enough CTAs for two per SM,
         at least two pages a slice."""
-        ctas = n * -(-self.heads // ops.LATENT_TILE_ROWS) * -(-self.kv_rank // 128)
+        ctas = n * -(-self.heads // ops.LATENT_TILE_ROWS) * -(-self.kv_rank // 256)
         pages = max(1, -(-ctx.max_context // PAGE_SIZE))
         want = -(-2 * ops.sm_count(self.device) // max(1, ctas * max(1, ctx.share)))
         return int(max(1, min(want, pages // 2, 64)))

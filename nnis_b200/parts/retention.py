@@ -11,6 +11,12 @@ the residual stream.  S [heads, dim, vdim] is float32, starts at zero and is the
 layer's whole memory of a sequence: it lives in the cache's state area, one per
 slot, so a later chunk or a single token goes on from what the tokens before left.
 
+Single tokens update the state in registers.  Prompts go 32 tokens at a time (the
+recurrence written as three small products per chunk, all float32); a long prompt is
+cut into runs of 256 tokens that start from zero side by side, after which the states
+between the runs are put together in order and every token receives what the tokens
+before its run contribute.
+
 params: hidden_size, heads, dim, vdim, decay (one per head), eps, position (a
 ``rope_frequencies`` PartSpec), names {q, k, v, g, o}.
 """
@@ -80,6 +86,17 @@ class Retention(Part):
         return 2.0 * sum(counts) * (W * 2 * H * (self.dim + self.vdim) + H * self.vdim * W
                                     + 2 * H * self.dim * self.vdim)
 
+    SEGMENTS, FIRST_SEGMENT = "retention/segments", "retention/first_segment"
+
+    def step_tables(self, counts, starts, have=()):
+        """Prompt steps with a sequence longer than a run: the runs of every sequence, worked
+        side by side (the same list for every retention layer of the model)."""
+        seg = ops.RETENTION_SEGMENT
+        if not ops.retention_takes_segments(self.dim) or max(counts) <= seg or self.SEGMENTS in have:
+            return {}
+        segments, first = ops.retention_segments(counts, seg)
+        return {self.SEGMENTS: segments, self.FIRST_SEGMENT: first}
+
     def forward(self, x: torch.Tensor, ctx, residual: torch.Tensor, cache: StateView) -> None:
         n = residual.shape[0]
         H, ws = self.heads, ctx.workspace
@@ -87,9 +104,14 @@ class Retention(Part):
         linear(x, self.w_in, None, qkvg, STORE, decode=ctx.decode)
         o_raw = ws.get("retention_o", (n, H * self.vdim), torch.float32)
         gated = ws.get("retention_gated", (n, H * self.vdim), self.dtype)
+        segments = ctx.tables.get(self.SEGMENTS) if ops.retention_takes_segments(self.dim) else None
+        seg_state = ws.get("retention_runs", (segments.shape[0], H, self.dim, self.vdim), torch.float32) \
+            if segments is not None else None
         ops.retention(qkvg, self.position.frequencies(), self._decay, cache.state, ctx.token_pos,
                       ctx.token_seq, ctx.seq_slots, ctx.seq_first_row, ctx.seq_start, ctx.seq_count,
-                      o_raw, gated, H, self.dim, self.vdim, self.position.dims, self.eps)
+                      o_raw, gated, H, self.dim, self.vdim, self.position.dims, self.eps,
+                      segments=segments, seq_first_segment=ctx.tables.get(self.FIRST_SEGMENT),
+                      seg_state=seg_state, seg_len=ops.RETENTION_SEGMENT)
         linear(gated, self.w_o, None, residual, ADD_F32, ws, decode=ctx.decode)
 
 

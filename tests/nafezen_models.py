@@ -55,12 +55,15 @@ ODD = config(200, 132, 1, 1e-6, [
     layer("latent_attention", latent(1, 10, 2, 6, 12, 20), None),
 ])
 # one mechanism each
-ONLY_LATENT = config(150, 64, 2, 1e-5, [layer("latent_attention", latent(4, 16, 16, 24, 32, 40), None)])
+ONLY_LATENT = config(150, 64, 2, 1e-5, [layer("latent_attention", latent(4, 16, 16, 24, 32, 48), None)])
 ONLY_RETENTION = config(150, 64, 4, 1e-5, [layer("retention", retention(2, 32, 48, [0.9375, 0.9990234375], 24), None)])
+# key size 64 with a decay near one: long prompts are cut into runs that are worked side by side
+LONG_RETENTION = config(150, 64, 1, 1e-5, [layer("retention", retention(3, 64, 40, [0.96875, 0.998046875, 0.9998779296875], 64),
+                                               dense(40))])
 ONLY_MOE = config(150, 72, 2, 1e-5, [layer("latent_attention", latent(2, 8, 8, 8, 16, 16), moe(7, 3, 40, shared=24))])
 ONLY_DENSE = config(150, 72, 3, 1e-5, [layer("retention", retention(1, 16, 16, [0.5], 8), dense(88))])
 CONFIGS: Dict[str, dict] = {"mixed": MIXED, "odd": ODD, "latent": ONLY_LATENT, "retention": ONLY_RETENTION,
-                            "moe": ONLY_MOE, "dense": ONLY_DENSE}
+                            "moe": ONLY_MOE, "dense": ONLY_DENSE, "long_retention": LONG_RETENTION}
 
 
 def make_model(tmp_dir: str, cfg: dict, seed: int, sharpen: float = 1.0) -> str:

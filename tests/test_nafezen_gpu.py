@@ -240,6 +240,27 @@ def test_long_decoding_over_page_borders(models, dtype, tmp_path):
     replay_and_check(models, "mixed", dtype, trace, {"a": toks}, tmp_path, "long decoding")
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_long_prompts_of_retention_in_runs_and_portions(models, dtype, tmp_path):
+    """Prompts longer than a run of the retention kernels (runs are worked side by side and
+    put together afterwards), alone, in a batch with short ones, continued after a first
+    portion, and decoded on: a state lost or joined wrongly at a run's edge shows, since the
+    slowest head forgets next to nothing over a thousand tokens."""
+    name = "long_retention"
+    vocab = read_config(models[name])["vocab"]
+    rng = random.Random(31)
+    a, b, c = (random_tokens(rng, n, vocab) for n in (700, 257, 40))
+    trace = TraceBuilder()
+    trace.step([("a", a[:690], [0, 255, 256, 257, 511, 512, 689])])
+    for t in range(690, 700):
+        trace.step([("a", a[t:t + 1], [0])], end=["a"] if t == 699 else [])
+    trace.step([("b", b[:100], [99]), ("c", c[:39], [38])])          # a first portion, then runs after it
+    trace.step([("b", b[100:], list(range(150, 157))), ("c", c[39:], [0])], end=["b", "c"])
+    trace.step([("a2", a, [256, 600, 699]), ("c2", c, [39]), ("b2", b, [255, 256])], end=["a2", "c2", "b2"])
+    replay_and_check(models, name, dtype, trace, {"a": a, "b": b, "c": c, "a2": a, "c2": c, "b2": b}, tmp_path,
+                     "runs")
+
+
 def test_far_keys_and_page_borders_with_sharp_attention(models, tmp_path):
     """Query up-projections times six: most of a query's weight lies on one key, and the
     plain implementation says which.  Among those keys are far ones and ones on both sides
