@@ -37,6 +37,8 @@ latent_prep_kernel(const float* __restrict__ a, const float* __restrict__ wq,
                    T* __restrict__ cache, int q_rank, int kv_rank, int rot, int rot_dims,
                    int page_size, float eps) {
     __shared__ float scratch[4];
+    pdl_wait();
+    pdl_launch_dependents();
     int n = blockIdx.x;
     int pos = token_pos[n];
     if (pos < 0) return;  // a padding row
@@ -195,17 +197,18 @@ NNIS_API int nnis_latent_prep(const float* a, const float* wq, const float* wkv,
         rot_dims > rot || page_size <= 0 || table_cols <= 0 || !(eps > 0.f) || !a || !wq || !wkv ||
         !freq || !cq || !cache)
         return NNIS_ERR_ARGUMENT;
+    cudaError_t e;
     if (dtype == NNIS_DTYPE_F32)
-        latent_prep_kernel<float><<<n_tokens, 128, 0, stream>>>(
-            a, wq, wkv, freq, token_pos, token_seq, page_table, table_cols, (float*)cq, (float*)cache,
-            q_rank, kv_rank, rot, rot_dims, page_size, eps);
+        e = launch_dependent(latent_prep_kernel<float>, n_tokens, 128, 0, stream, a, wq, wkv, freq, token_pos,
+                             token_seq, page_table, table_cols, (float*)cq, (float*)cache, q_rank, kv_rank, rot,
+                             rot_dims, page_size, eps);
     else if (dtype == NNIS_DTYPE_BF16)
-        latent_prep_kernel<bf16><<<n_tokens, 128, 0, stream>>>(
-            a, wq, wkv, freq, token_pos, token_seq, page_table, table_cols, (bf16*)cq, (bf16*)cache,
-            q_rank, kv_rank, rot, rot_dims, page_size, eps);
+        e = launch_dependent(latent_prep_kernel<bf16>, n_tokens, 128, 0, stream, a, wq, wkv, freq, token_pos,
+                             token_seq, page_table, table_cols, (bf16*)cq, (bf16*)cache, q_rank, kv_rank, rot,
+                             rot_dims, page_size, eps);
     else
         return NNIS_ERR_UNSUPPORTED;
-    NNIS_RETURN_LAUNCH();
+    return e == cudaSuccess ? NNIS_OK : (int)e;
 }
 
 // Scratch: `partial` needs n_tokens * heads * n_splits * (dv + 2) floats when

@@ -40,6 +40,8 @@ latent_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ cache,
                   float scale, int n_splits) {
     constexpr int NT = kLatChunk / 8;
     extern __shared__ __align__(128) unsigned char smem_raw[];
+    pdl_wait();
+    pdl_launch_dependents();
     bf16* q_s = reinterpret_cast<bf16*>(smem_raw);       // [64, dkp] swizzled
     bf16* k_s = q_s + (size_t)kLatRows * dkp;            // stages x [64, dkp]
     // eight warps: warps 0-3 and 4-7 own the same 64 rows and two runs of output values
@@ -294,15 +296,15 @@ NNIS_API int nnis_attention_latent_mma(const void* q, const void* cache, const i
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
     }
-    kernel<<<grid, 256, smem, stream>>>((const bf16*)q, (const bf16*)cache, tiles, seq_first_row, seq_start,
-                                        seq_count, token_pos, token_seq, page_table, table_cols, (bf16*)out,
-                                        partial, heads, dk, dv, dkp, tiles_per_token, scale, n_splits);
-    cudaError_t e = cudaGetLastError();
+    cudaError_t e = launch_dependent(kernel, grid, 256, smem, stream, (const bf16*)q, (const bf16*)cache, tiles,
+                                     seq_first_row, seq_start, seq_count, token_pos, token_seq, page_table,
+                                     table_cols, (bf16*)out, partial, heads, dk, dv, dkp, tiles_per_token, scale,
+                                     n_splits);
     if (e != cudaSuccess) return (int)e;
     if (n_splits > 1) {
         size_t rows = (size_t)n_tokens * heads;
-        attn_merge_kernel<bf16><<<(unsigned)rows, 128, 0, stream>>>(partial, (bf16*)out, rows, dv,
-                                                                                n_splits);
+        e = launch_dependent(attn_merge_kernel<bf16>, (unsigned)rows, 128, 0, stream, (const float*)partial,
+                             (bf16*)out, rows, dv, n_splits);
     }
-    NNIS_RETURN_LAUNCH();
+    return e == cudaSuccess ? NNIS_OK : (int)e;
 }

@@ -5,6 +5,7 @@
 
 #include <float.h>
 
+#include "async_copy.cuh"
 #include "common.cuh"
 
 namespace nnis {
@@ -17,6 +18,8 @@ __global__ void __launch_bounds__(128)
 attn_merge_kernel(const float* __restrict__ partial, T* __restrict__ out, size_t n_rows, int d,
                   int n_splits) {
     __shared__ float share[64];
+    pdl_wait();  // (a no-op unless launched as a programmatic dependent)
+    pdl_launch_dependents();
     const int lane = threadIdx.x & 31;
     const size_t row = blockIdx.x;
     const float* rec = partial + row * n_splits * (size_t)(d + 2);

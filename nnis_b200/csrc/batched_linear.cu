@@ -6,6 +6,7 @@
 // load) and to carry the attention's latent output to the heads' values.
 // Operands float32 or bfloat16, float32 accumulation with fmaf on the CUDA cores
 // (the float32 path, and the bfloat16 path of shapes the tensor-core kernel refuses).
+#include "async_copy.cuh"
 #include "common.cuh"
 
 namespace nnis {
@@ -64,6 +65,8 @@ template <typename T>
 __global__ void __launch_bounds__(256)
 batched_rows_kernel(const T* __restrict__ A, long long lda, long long a_bs, const T* __restrict__ W,
                     T* __restrict__ C, long long ldc, long long c_bs, int M, int N, int K) {
+    pdl_wait();
+    pdl_launch_dependents();
     int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     int n = blockIdx.x * 8 + warp, b = blockIdx.z, m0 = blockIdx.y * 8;
     if (n >= N) return;
@@ -89,8 +92,9 @@ static int launch_batched(const void* A, long long lda, long long a_bs, const vo
                           cudaStream_t stream) {
     if (M <= 16) {
         dim3 grid((N + 7) / 8, (M + 7) / 8, batch);
-        batched_rows_kernel<T><<<grid, 256, 0, stream>>>((const T*)A, lda, a_bs, (const T*)W, (T*)C,
-                                                         ldc, c_bs, M, N, K);
+        cudaError_t e = launch_dependent(batched_rows_kernel<T>, grid, 256, 0, stream, (const T*)A, lda, a_bs,
+                                         (const T*)W, (T*)C, ldc, c_bs, M, N, K);
+        return e == cudaSuccess ? NNIS_OK : (int)e;
     } else {
         dim3 grid((N + 63) / 64, (M + 63) / 64, batch);
         if (grid.y > 65535u) return NNIS_ERR_UNSUPPORTED;

@@ -84,6 +84,29 @@ __device__ __forceinline__ float warp_max(float v) {
     return v;
 }
 
+// Whether kernels are launched as programmatic dependents of the kernel before them
+// (NNIS_PDL=0 turns it off everywhere); defined in elementwise.cu.
+bool dependent_launches();
+
+// Launch `kernel` as a programmatic dependent of the kernel before it on the stream: it may
+// be scheduled while that kernel still runs and waits for it with griddepcontrol.wait (the
+// kernel must call pdl_wait() before it touches anything a kernel of the step writes).
+template <typename... Params, typename... Args>
+inline cudaError_t launch_dependent(void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem,
+                                    cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = dependent_launches() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<Params>(args)...);
+}
+
 // The timeline of a step (trace.cu): the next slot of the trace buffer for a launch
 // of the named kernel, or null when no trace is being taken.
 unsigned long long* trace_slot(const char* name);

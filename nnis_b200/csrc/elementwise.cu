@@ -6,7 +6,18 @@
 #include "async_copy.cuh"
 #include "common.cuh"
 
+#include <stdlib.h>
+#include <string.h>
+
 namespace nnis {
+
+bool dependent_launches() {
+    static const bool on = [] {
+        const char* v = getenv("NNIS_PDL");
+        return !(v && strcmp(v, "0") == 0);
+    }();
+    return on;
+}
 
 // ---------------------------------------------------------------------------
 // hidden[n, :] = table[token[n], :]  (widened exactly to float32)
@@ -196,6 +207,8 @@ __global__ void __launch_bounds__(256)
 group_rmsnorm_kernel(const float* x, const int* __restrict__ rows,
                      const float* __restrict__ w, T* y, long long n_units, int width, int groups,
                      float eps) {
+    pdl_wait();
+    pdl_launch_dependents();
     long long unit = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
     if (unit >= n_units) return;
     int lane = threadIdx.x & 31;
@@ -220,6 +233,8 @@ group_rmsnorm_kernel(const float* x, const int* __restrict__ rows,
 template <typename T>
 __global__ void relu2_gate_kernel(const float* __restrict__ u, T* __restrict__ out, size_t n_rows,
                                   int inter, int gated) {
+    pdl_wait();
+    pdl_launch_dependents();
     size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= n_rows * (size_t)inter) return;
     size_t n = idx / inter;
@@ -242,6 +257,8 @@ __global__ void rope_part_kernel(const T* __restrict__ src, long long src_row, i
                                  int src_off, T* __restrict__ dst, long long dst_row, int dst_head,
                                  int dst_off, const int* __restrict__ token_pos,
                                  const float* __restrict__ freq, int heads, int len, int dims) {
+    pdl_wait();
+    pdl_launch_dependents();
     int n = blockIdx.x;
     int pos = token_pos[n];
     int half = dims >> 1;
@@ -368,15 +385,16 @@ NNIS_API int nnis_group_rmsnorm(const float* x, const int* rows, const float* w,
         return NNIS_ERR_ARGUMENT;
     long long units = (long long)n_rows * groups;
     unsigned blocks = (unsigned)((units + 7) / 8);
+    cudaError_t e;
     if (out_dtype == NNIS_DTYPE_F32)
-        group_rmsnorm_kernel<float><<<blocks, 256, 0, stream>>>(x, rows, w, (float*)y, units, width,
-                                                                groups, eps);
+        e = launch_dependent(group_rmsnorm_kernel<float>, blocks, 256, 0, stream, x, rows, w, (float*)y, units,
+                             width, groups, eps);
     else if (out_dtype == NNIS_DTYPE_BF16)
-        group_rmsnorm_kernel<bf16><<<blocks, 256, 0, stream>>>(x, rows, w, (bf16*)y, units, width,
-                                                               groups, eps);
+        e = launch_dependent(group_rmsnorm_kernel<bf16>, blocks, 256, 0, stream, x, rows, w, (bf16*)y, units,
+                             width, groups, eps);
     else
         return NNIS_ERR_UNSUPPORTED;
-    NNIS_RETURN_LAUNCH();
+    return e == cudaSuccess ? NNIS_OK : (int)e;
 }
 
 NNIS_API int nnis_relu2_gate(const float* u, void* out, int out_dtype, long long n_rows, int inter,
@@ -384,13 +402,16 @@ NNIS_API int nnis_relu2_gate(const float* u, void* out, int out_dtype, long long
     if (n_rows <= 0 || inter <= 0 || gated < 0) return NNIS_ERR_ARGUMENT;
     size_t total = (size_t)n_rows * inter;
     unsigned blocks = (unsigned)((total + 255) / 256);
+    cudaError_t e;
     if (out_dtype == NNIS_DTYPE_F32)
-        relu2_gate_kernel<float><<<blocks, 256, 0, stream>>>(u, (float*)out, n_rows, inter, gated);
+        e = launch_dependent(relu2_gate_kernel<float>, blocks, 256, 0, stream, u, (float*)out, (size_t)n_rows, inter,
+                             gated);
     else if (out_dtype == NNIS_DTYPE_BF16)
-        relu2_gate_kernel<bf16><<<blocks, 256, 0, stream>>>(u, (bf16*)out, n_rows, inter, gated);
+        e = launch_dependent(relu2_gate_kernel<bf16>, blocks, 256, 0, stream, u, (bf16*)out, (size_t)n_rows, inter,
+                             gated);
     else
         return NNIS_ERR_UNSUPPORTED;
-    NNIS_RETURN_LAUNCH();
+    return e == cudaSuccess ? NNIS_OK : (int)e;
 }
 
 NNIS_API int nnis_rope_part(const void* src, long long src_row, int src_head, int src_off, void* dst,
@@ -401,15 +422,16 @@ NNIS_API int nnis_rope_part(const void* src, long long src_row, int src_head, in
         return NNIS_ERR_ARGUMENT;
     int work = heads * (len - dims / 2);
     int threads = work >= 256 ? 256 : (work >= 128 ? 128 : 64);
+    cudaError_t e;
     if (dtype == NNIS_DTYPE_F32)
-        rope_part_kernel<float><<<n_tokens, threads, 0, stream>>>(
-            (const float*)src, src_row, src_head, src_off, (float*)dst, dst_row, dst_head, dst_off,
-            token_pos, freq, heads, len, dims);
+        e = launch_dependent(rope_part_kernel<float>, n_tokens, threads, 0, stream, (const float*)src, src_row,
+                             src_head, src_off, (float*)dst, dst_row, dst_head, dst_off, token_pos, freq, heads,
+                             len, dims);
     else if (dtype == NNIS_DTYPE_BF16)
-        rope_part_kernel<bf16><<<n_tokens, threads, 0, stream>>>(
-            (const bf16*)src, src_row, src_head, src_off, (bf16*)dst, dst_row, dst_head, dst_off,
-            token_pos, freq, heads, len, dims);
+        e = launch_dependent(rope_part_kernel<bf16>, n_tokens, threads, 0, stream, (const bf16*)src, src_row,
+                             src_head, src_off, (bf16*)dst, dst_row, dst_head, dst_off, token_pos, freq, heads,
+                             len, dims);
     else
         return NNIS_ERR_UNSUPPORTED;
-    NNIS_RETURN_LAUNCH();
+    return e == cudaSuccess ? NNIS_OK : (int)e;
 }

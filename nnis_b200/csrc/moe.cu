@@ -12,6 +12,7 @@
 // A row whose position is -1 (padding) is skipped everywhere.
 #include <float.h>
 
+#include "async_copy.cuh"
 #include "common.cuh"
 
 namespace nnis {
@@ -22,6 +23,8 @@ moe_route_kernel(const T* __restrict__ h, const float* __restrict__ wr, const fl
                  const int* __restrict__ token_pos, int* __restrict__ ids,
                  float* __restrict__ weights, int n_tokens, int width, int experts, int top) {
     extern __shared__ float z[];  // [experts]
+    pdl_wait();
+    pdl_launch_dependents();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int n = blockIdx.x;
     int* id = ids + (size_t)n * top;
@@ -83,6 +86,8 @@ template <typename T>
 __global__ void __launch_bounds__(256)
 moe_up_kernel(const T* __restrict__ h, const T* __restrict__ w_up, const int* __restrict__ ids,
               const int* __restrict__ token_pos, T* __restrict__ act, int width, int ff, int top) {
+    pdl_wait();
+    pdl_launch_dependents();
     int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     long long pair = blockIdx.x;
     int f = blockIdx.y * 8 + warp;
@@ -104,6 +109,8 @@ __global__ void __launch_bounds__(256)
 moe_down_kernel(const T* __restrict__ act, const T* __restrict__ w_down, const int* __restrict__ ids,
                 const float* __restrict__ weights, const int* __restrict__ token_pos,
                 float* __restrict__ residual, int width, int ff, int top) {
+    pdl_wait();
+    pdl_launch_dependents();
     int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     long long n = blockIdx.x;
     int c = blockIdx.y * 8 + warp;
@@ -133,15 +140,16 @@ NNIS_API int nnis_moe_route(const void* h, const float* wr, const float* br, con
     size_t smem = (size_t)experts * sizeof(float);
     if (smem > 48 * 1024) return NNIS_ERR_UNSUPPORTED;
     unsigned blocks = (unsigned)n_tokens;
+    cudaError_t e;
     if (dtype == NNIS_DTYPE_F32)
-        moe_route_kernel<float><<<blocks, 256, smem, stream>>>((const float*)h, wr, br, token_pos, ids,
-                                                               weights, n_tokens, width, experts, top);
+        e = launch_dependent(moe_route_kernel<float>, blocks, 256, smem, stream, (const float*)h, wr, br, token_pos,
+                             ids, weights, n_tokens, width, experts, top);
     else if (dtype == NNIS_DTYPE_BF16)
-        moe_route_kernel<bf16><<<blocks, 256, smem, stream>>>((const bf16*)h, wr, br, token_pos, ids,
-                                                              weights, n_tokens, width, experts, top);
+        e = launch_dependent(moe_route_kernel<bf16>, blocks, 256, smem, stream, (const bf16*)h, wr, br, token_pos,
+                             ids, weights, n_tokens, width, experts, top);
     else
         return NNIS_ERR_UNSUPPORTED;
-    NNIS_RETURN_LAUNCH();
+    return e == cudaSuccess ? NNIS_OK : (int)e;
 }
 
 // act: operand dtype [n_tokens, top, ff] (scratch); residual: float32 [n_tokens, width]
@@ -155,20 +163,21 @@ NNIS_API int nnis_moe_experts(const void* h, const void* w_up, const void* w_dow
     if ((ff + 7) / 8 > 65535 || (width + 7) / 8 > 65535) return NNIS_ERR_UNSUPPORTED;
     dim3 up_grid((unsigned)((long long)n_tokens * top), (ff + 7) / 8);
     dim3 down_grid(n_tokens, (width + 7) / 8);
+    cudaError_t e;
     if (dtype == NNIS_DTYPE_F32) {
-        moe_up_kernel<float><<<up_grid, 256, 0, stream>>>((const float*)h, (const float*)w_up, ids,
-                                                          token_pos, (float*)act, width, ff, top);
-        moe_down_kernel<float><<<down_grid, 256, 0, stream>>>((const float*)act, (const float*)w_down,
-                                                              ids, weights, token_pos, residual, width,
-                                                              ff, top);
+        e = launch_dependent(moe_up_kernel<float>, up_grid, 256, 0, stream, (const float*)h, (const float*)w_up, ids,
+                             token_pos, (float*)act, width, ff, top);
+        if (e == cudaSuccess)
+            e = launch_dependent(moe_down_kernel<float>, down_grid, 256, 0, stream, (const float*)act,
+                                 (const float*)w_down, ids, weights, token_pos, residual, width, ff, top);
     } else if (dtype == NNIS_DTYPE_BF16) {
-        moe_up_kernel<bf16><<<up_grid, 256, 0, stream>>>((const bf16*)h, (const bf16*)w_up, ids,
-                                                         token_pos, (bf16*)act, width, ff, top);
-        moe_down_kernel<bf16><<<down_grid, 256, 0, stream>>>((const bf16*)act, (const bf16*)w_down, ids,
-                                                             weights, token_pos, residual, width, ff,
-                                                             top);
+        e = launch_dependent(moe_up_kernel<bf16>, up_grid, 256, 0, stream, (const bf16*)h, (const bf16*)w_up, ids,
+                             token_pos, (bf16*)act, width, ff, top);
+        if (e == cudaSuccess)
+            e = launch_dependent(moe_down_kernel<bf16>, down_grid, 256, 0, stream, (const bf16*)act,
+                                 (const bf16*)w_down, ids, weights, token_pos, residual, width, ff, top);
     } else {
         return NNIS_ERR_UNSUPPORTED;
     }
-    NNIS_RETURN_LAUNCH();
+    return e == cudaSuccess ? NNIS_OK : (int)e;
 }

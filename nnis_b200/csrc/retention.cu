@@ -13,6 +13,7 @@
 //   retention_gate   o / rms(o) per head, times silu(g), rounded once.
 //
 // Packed input rows: [q (H dim) | k (H dim) | v (H vdim) | g (H vdim)].
+#include "async_copy.cuh"
 #include "common.cuh"
 
 namespace nnis {
@@ -26,6 +27,8 @@ retention_scan_kernel(const T* __restrict__ qkvg, const float* __restrict__ freq
                       const int* __restrict__ seq_start, const int* __restrict__ seq_count,
                       float* __restrict__ o_raw, int heads, int dim, int vdim, int rot_dims) {
     extern __shared__ float smem[];
+    pdl_wait();
+    pdl_launch_dependents();
     float* qs = smem;             // [dim]
     float* ks = smem + dim;       // [dim]
     float* red = smem + 2 * dim;  // [8][32]
@@ -374,6 +377,8 @@ __global__ void __launch_bounds__(256)
 retention_gate_kernel(const float* __restrict__ o_raw, const T* __restrict__ qkvg,
                       const int* __restrict__ token_pos, T* __restrict__ out, long long n_units,
                       int heads, int dim, int vdim, float eps) {
+    pdl_wait();
+    pdl_launch_dependents();
     long long unit = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
     if (unit >= n_units) return;
     int lane = threadIdx.x & 31;
@@ -448,21 +453,21 @@ static int launch_retention(const void* qkvg, const float* freq, const float* de
         NNIS_RETURN_LAUNCH();
     }
     size_t smem = (2 * (size_t)dim + 256) * sizeof(float);
+    cudaError_t le = cudaSuccess;
 #define NNIS_RET_CASE(R) \
-    retention_scan_kernel<T, R><<<grid, 256, smem, stream>>>( \
-        (const T*)qkvg, freq, decay, state, token_pos, token_seq, seq_slots, seq_first_row, seq_start, \
-        seq_count, o_raw, heads, dim, vdim, rot_dims)
+    le = launch_dependent(retention_scan_kernel<T, R>, grid, 256, smem, stream, (const T*)qkvg, freq, decay, state, \
+                          token_pos, token_seq, seq_slots, seq_first_row, seq_start, seq_count, o_raw, heads, dim, \
+                          vdim, rot_dims)
     if (dim <= 32) NNIS_RET_CASE(4);
     else if (dim <= 64) NNIS_RET_CASE(8);
     else if (dim <= 128) NNIS_RET_CASE(16);
     else NNIS_RET_CASE(32);
 #undef NNIS_RET_CASE
-    cudaError_t e = cudaGetLastError();
-    if (e != cudaSuccess) return (int)e;
+    if (le != cudaSuccess) return (int)le;
     long long units = (long long)n_tokens * heads;
-    retention_gate_kernel<T><<<(unsigned)((units + 7) / 8), 256, 0, stream>>>(
-        o_raw, (const T*)qkvg, token_pos, (T*)out, units, heads, dim, vdim, eps);
-    NNIS_RETURN_LAUNCH();
+    le = launch_dependent(retention_gate_kernel<T>, (unsigned)((units + 7) / 8), 256, 0, stream,
+                          (const float*)o_raw, (const T*)qkvg, token_pos, (T*)out, units, heads, dim, vdim, eps);
+    return le == cudaSuccess ? NNIS_OK : (int)le;
 }
 
 }  // namespace nnis
