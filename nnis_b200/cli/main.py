@@ -279,7 +279,7 @@ def validate(a: GenerateArgs, out=sys.stdout) -> int:
         config = read_config(a.model_dir)
         spec = config.to_spec()
         raw = config.to_dict()
-        report["architecture"] = (raw.get("architectures") or [None])[0]
+        report["architecture"] = spec.architecture
         report["model_type"] = raw.get("model_type")
         report["vocab_size"] = spec.vocab_size
         report["layers"] = len(spec.schedule)

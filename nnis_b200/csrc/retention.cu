@@ -285,10 +285,21 @@ retention_prefix_kernel(float* __restrict__ seg_state, float* __restrict__ state
     const float g = decay[h];
     float* cell = state + ((size_t)seq_slots[b] * heads + h) * per_head + e;
     float run = *cell;
+    // g^32 and g^seg_len as the chunk kernel's chain of products makes them
+    float g32 = 1.f;
+    for (int n = 0; n < 32; ++n) g32 *= g;
+    float g_run = 1.f;
+    for (int n = 0; n < seg_len / 32; ++n) g_run *= g32;
     for (int s = s0; s < s1; ++s) {
         int len = min(seg_len, count - (s - s0) * seg_len);
-        float p = 1.f;
-        for (int n = 0; n < len; ++n) p *= g;
+        float p = g_run;
+        if (len < seg_len) {  // the last, shorter run: whole chunks, then the rest
+            p = 1.f;
+            for (int n = 0; n < len / 32; ++n) p *= g32;
+            float rest = 1.f;
+            for (int n = 0; n < len % 32; ++n) rest *= g;
+            p *= rest;
+        }
         float* u = seg_state + ((size_t)s * heads + h) * per_head + e;
         float after = fmaf(p, run, *u);
         *u = run;

@@ -121,7 +121,7 @@ class LatentAttention(Part):
         rows each; the same for every layer with this number of heads."""
         if not self._tensor_cores() or self._tiles_name() in have:
             return {}
-        return {self._tiles_name(): ops.latent_tiles(counts, self.heads)}
+        return {self._tiles_name(): ops.latent_tiles(counts, starts, self.heads)}
 
     def _decode_splits(self, ctx, n: int) -> int:
         """Slices of the key range in a step of single tokens: enough CTAs for two per SM,

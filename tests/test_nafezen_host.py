@@ -70,6 +70,18 @@ def test_loader_reports_every_fault_of_a_folder(tmp_path):
     assert "l1.mlp.router.b" in str(e.value) and "l0.mix.uk" in str(e.value) and "l9.extra" in str(e.value)
 
 
+def test_command_line_writes_and_validates_a_model_folder(tmp_path):
+    from nnis_b200.cli.main import main
+    cfg = tmp_path / "config.json"
+    cfg.write_text(json.dumps(ODD))
+    out = tmp_path / "model"
+    assert main(["random-model", "--config", str(cfg), "--seed", "9", "--out", str(out)]) == 0
+    report = tmp_path / "report.json"
+    assert main(["validate", "--model", str(out), "--json", "--output", str(report)]) == 0
+    seen = json.loads(report.read_text())
+    assert seen["ready"] and seen["architecture"] == "Nafezen" and seen["layers"] == 3
+
+
 # ---- the plain implementation's mechanisms against closed forms ---------------------
 def test_plain_grouped_norm():
     x = torch.randn(5, 12, dtype=F)
