@@ -267,6 +267,36 @@ def design_configs(size: str):
     return llama, nafezen
 
 
+def profile_steps(args) -> int:
+    """For a profiler (``--designs s --profile-steps N``): N prompt steps of 2,048 tokens and N
+    decode steps of 8 sequences at context 2,000 of the first four Nafezen layers, run eagerly
+    (no CUDA graph) so that every launch is there to be captured; nothing is timed."""
+    import torch
+
+    import nnis_b200.engine.engine as engine_module
+    from nnis_b200.engine import Engine, SequenceStep
+    from nnis_b200.weights import write_random_model
+    engine_module.GRAPH_MIN_TOKENS = 1 << 30
+    _, cfg = design_configs(args.designs.split(",")[0])
+    cfg["layers"] = cfg["layers"][:4]
+    rng = random.Random(0)
+    with tempfile.TemporaryDirectory() as tmp:
+        write_random_model(cfg, seed=0, out_dir=tmp, std=1.0, norm_std=0.1, std_by_fan_in=True)
+        engine = Engine.from_dir(tmp, dtype="bfloat16", max_tokens=8 * 2200 + 4096)
+    prompt = [rng.randrange(cfg["vocab"]) for _ in range(2048)]
+    for _ in range(args.profile_steps):
+        slot = engine.acquire_slot()
+        engine.step([SequenceStep(slot, prompt, [2047])])
+        engine.release_slot(slot)
+    slots = [engine.acquire_slot() for _ in range(8)]
+    engine.step([SequenceStep(s, prompt[:2000], []) for s in slots])
+    for _ in range(args.profile_steps):
+        engine.step([SequenceStep(s, [5], [0]) for s in slots])
+    torch.cuda.synchronize()
+    print(json.dumps({"profile_steps": args.profile_steps, "layers": 4, "design": "nafezen"}))
+    return 0
+
+
 def compare_designs(args) -> int:
     """Prefill and decode of both designs at each size, with the time of every part of a
     prompt step (CUDA events around the part, one eager step) against the part's own
@@ -404,9 +434,12 @@ def main() -> int:
     ap.add_argument("--designs", metavar="SIZES", default=None,
                     help="instead of the benchmark: the Nafezen design beside the Llama decoder at equal "
                          "width and depth, sizes 's' and/or 'm' with commas: prefill, its parts, decoding")
+    ap.add_argument("--profile-steps", type=int, default=0,
+                    help="with --designs: run this many eager prompt and decode steps of the Nafezen model "
+                         "for a profiler instead of the timed comparison")
     args = ap.parse_args()
     if args.designs:
-        return compare_designs(args)
+        return profile_steps(args) if args.profile_steps > 0 else compare_designs(args)
     CONTEXT = max(args.context, 64)
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":

@@ -287,6 +287,66 @@ def test_far_keys_and_page_borders_with_sharp_attention(models, tmp_path):
         replay_and_check(models, "sharp", dtype, trace, {"w": toks, "d": toks}, tmp_path, "sharp")
 
 
+def _random_config(rng):
+    """Sizes, layer order, heads, experts and constants drawn at random (small ones)."""
+    from nafezen_models import config, dense, latent, layer, moe, retention
+    groups = rng.choice([1, 2, 3, 4, 6])
+    width = groups * rng.choice([8, 12, 16, 20, 24, 32, 40, 48])
+    layers = []
+    for _ in range(rng.randint(1, 5)):
+        if rng.random() < 0.6:
+            mixer = latent(rng.randint(1, 9), rng.choice([4, 8, 10, 16, 24, 32, 64]), rng.choice([2, 4, 8, 16, 32]),
+                           rng.choice([4, 6, 8, 16, 24, 32, 64]), rng.choice([8, 16, 24, 40, 64, 100, 128]),
+                           rng.choice([8, 16, 20, 32, 48, 64, 96, 128]), base=rng.choice([100.0, 10000.0, 500000.0]))
+            kind = "latent_attention"
+        else:
+            dim, heads = rng.choice([8, 16, 24, 32, 48, 64, 128]), rng.randint(1, 4)
+            mixer = retention(heads, dim, rng.choice([8, 16, 32, 40, 64, 96]),
+                              [1 - 2.0 ** -rng.randint(1, 12) for _ in range(heads)],
+                              rng.choice([d for d in (2, 4, 8, 16, 32, 64, 128, dim) if d <= dim]),
+                              base=rng.choice([10.0, 10000.0, 1e6]))
+            kind = "retention"
+        r = rng.random()
+        if r < 0.2:
+            ff = None
+        elif r < 0.5:
+            ff = dense(rng.choice([8, 16, 40, 64, 96, 136]))
+        else:
+            experts = rng.randint(1, 16)
+            ff = moe(experts, rng.randint(1, experts), rng.choice([8, 12, 16, 24, 40, 64]),
+                     shared=rng.choice([None, 7, 8, 16, 40]))
+        layers.append(layer(kind, mixer, ff))
+    return config(rng.choice([50, 131, 256, 577]), width, groups, rng.choice([1e-5, 1e-6]), layers)
+
+
+@pytest.mark.parametrize("trial", range(8))
+def test_configurations_drawn_at_random(trial, tmp_path):
+    """A prompt in one step and six tokens one by one, both dtypes, on a model whose sizes,
+    layer order and constants are drawn at random: whatever kernels the sizes select."""
+    from nnis_b200.engine import Engine, SequenceStep
+    rng = random.Random(5000 + trial)
+    cfg = _random_config(rng)
+    d = make_model(str(tmp_path / "m"), cfg, seed=trial)
+    n = rng.choice([1, 5, 40, 70, 130, 300])
+    toks = random_tokens(rng, n + 6, cfg["vocab"])
+    for dtype in DTYPES:
+        bf = dtype == "bfloat16"
+        margins = []
+        want = P.forward(cfg, load_weights(d, bf), toks, emulate_bf16=bf, margins=margins)
+        keep = torch.ones(len(toks), dtype=torch.bool)
+        if bf and margins:
+            keep = torch.stack(margins).min(dim=0).values >= CLOSE_CALL
+        engine = Engine.from_dir(d, dtype=dtype, max_tokens=1024)
+        slot = engine.acquire_slot()
+        got = [engine.step([SequenceStep(slot, toks[:n], list(range(n)))]).cpu().numpy()]
+        for t in range(n, n + 6):
+            got.append(engine.step([SequenceStep(slot, toks[t:t + 1], [0])]).cpu().numpy())
+        engine.check_status()
+        got = np.concatenate(got)
+        if bool(keep.any()):
+            check_logits(got[keep.numpy()], want[keep], dtype, f"random configuration {trial} {dtype}: {json.dumps(cfg)}")
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_greedy_generation_through_the_entry_point(models, dtype):
     from nnis_b200 import LLM
