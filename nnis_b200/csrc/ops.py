@@ -1141,7 +1141,11 @@ def moe_experts(h: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor, ids: 
 
 
 LATENT_MMA = 0 if os.environ.get("NNIS_LATENT_MMA", "1") == "0" else 1
-LATENT_TILE_ROWS = 64  # stacked (token, head) rows per CTA of attention_latent_mma
+
+
+def latent_tile_rows(dv: int) -> int:
+    """Stacked (token, head) rows per CTA of ``attention_latent_mma`` for output rows of dv values."""
+    return int(_lib().nnis_attention_latent_mma_tile_rows(dv))
 
 
 def attention_latent_mma_takes(dk: int, dv: int, page_size: int) -> bool:
@@ -1149,13 +1153,14 @@ def attention_latent_mma_takes(dk: int, dv: int, page_size: int) -> bool:
     return bool(LATENT_MMA) and bool(_lib().nnis_attention_latent_mma_takes(dk, dv, page_size))
 
 
-def latent_tiles(counts, starts, heads: int):
+def latent_tiles(counts, starts, heads: int, tile_rows: int):
     """The work list of ``attention_latent_mma`` for a prompt step: (sequence, first stacked
-    row) per 64 rows of each sequence's tokens * heads rows, the tiles with the most pages to
-    walk first (a causal prompt's last tiles are its longest: begun last they would run alone)."""
+    row) per ``tile_rows`` rows of each sequence's tokens * heads rows, the tiles with the most
+    pages to walk first (a causal prompt's last tiles are its longest: begun last they would
+    run alone)."""
     import numpy as np
-    tiles = [(i, r0) for i, c in enumerate(counts) for r0 in range(0, int(c) * heads, LATENT_TILE_ROWS)]
-    tiles.sort(key=lambda t: -(int(starts[t[0]]) + (t[1] + LATENT_TILE_ROWS - 1) // heads))
+    tiles = [(i, r0) for i, c in enumerate(counts) for r0 in range(0, int(c) * heads, tile_rows)]
+    tiles.sort(key=lambda t: -(int(starts[t[0]]) + (t[1] + tile_rows - 1) // heads))
     return np.asarray(tiles, dtype=np.int32).reshape(-1, 2)
 
 

@@ -111,22 +111,23 @@ class LatentAttention(Part):
 
     # -- work lists ---------------------------------------------------------
     def _tiles_name(self) -> str:
-        return f"latent_mma/heads{self.heads}"
+        return f"latent_mma/heads{self.heads}/rows{ops.latent_tile_rows(self.kv_rank)}"
 
     def _tensor_cores(self) -> bool:
         return self.dtype == torch.bfloat16 and ops.attention_latent_mma_takes(self.row, self.kv_rank, PAGE_SIZE)
 
     def step_tables(self, counts, starts, have=()):
-        """The tiles of the tensor-core kernel for a prompt step: 64 stacked (token, head)
-        rows each; the same for every layer with this number of heads."""
+        """The tiles of the tensor-core kernel for a prompt step: 64 or 128 stacked (token,
+        head) rows each; the same for every layer with this number of heads and tile."""
         if not self._tensor_cores() or self._tiles_name() in have:
             return {}
-        return {self._tiles_name(): ops.latent_tiles(counts, starts, self.heads)}
+        return {self._tiles_name(): ops.latent_tiles(counts, starts, self.heads,
+                                                     ops.latent_tile_rows(self.kv_rank))}
 
     def _decode_splits(self, ctx, n: int) -> int:
         """Slices of the key range in a step of single tokens: enough CTAs for two per SM,
         at least two pages a slice."""
-        ctas = n * -(-self.heads // ops.LATENT_TILE_ROWS) * -(-self.kv_rank // 256)
+        ctas = n * -(-self.heads // ops.latent_tile_rows(self.kv_rank)) * -(-self.kv_rank // 512)
         pages = max(1, -(-ctx.max_context // PAGE_SIZE))
         want = -(-2 * ops.sm_count(self.device) // max(1, ctas * max(1, ctx.share)))
         return int(max(1, min(want, pages // 2, 64)))

@@ -62,8 +62,12 @@ LONG_RETENTION = config(150, 64, 1, 1e-5, [layer("retention", retention(3, 64, 4
                                                dense(40))])
 ONLY_MOE = config(150, 72, 2, 1e-5, [layer("latent_attention", latent(2, 8, 8, 8, 16, 16), moe(7, 3, 40, shared=24))])
 ONLY_DENSE = config(150, 72, 3, 1e-5, [layer("retention", retention(1, 16, 16, [0.5], 8), dense(88))])
+# latents wider than one run of the tensor-core attention's output values (128), and wider than two
+WIDE_LATENT = config(150, 64, 1, 1e-5, [layer("latent_attention", latent(3, 16, 16, 24, 32, 192), None),
+                                        layer("latent_attention", latent(2, 24, 16, 16, 40, 320), dense(48))])
 CONFIGS: Dict[str, dict] = {"mixed": MIXED, "odd": ODD, "latent": ONLY_LATENT, "retention": ONLY_RETENTION,
-                            "moe": ONLY_MOE, "dense": ONLY_DENSE, "long_retention": LONG_RETENTION}
+                            "moe": ONLY_MOE, "dense": ONLY_DENSE, "long_retention": LONG_RETENTION,
+                            "wide_latent": WIDE_LATENT}
 
 
 def make_model(tmp_dir: str, cfg: dict, seed: int, sharpen: float = 1.0) -> str:
