@@ -310,15 +310,20 @@ def compare_designs(args) -> int:
     pk = peaks()
     rng = random.Random(0)
     prompt_len, context, batch = 2048, 2048, 8
+    clocks = ClockSampler(gpu_identity(torch))
+    clocks.start()
+    windows = []
 
     def timed(fn, n):
         start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         torch.cuda.synchronize()
+        t0 = clocks.mark()
         start.record()
         for _ in range(n):
             fn()
         end.record()
         torch.cuda.synchronize()
+        windows.append((t0, clocks.mark()))
         return start.elapsed_time(end) / n
 
     for size in args.designs.split(","):
@@ -330,6 +335,7 @@ def compare_designs(args) -> int:
             engine = llm.engine
             vocab = engine.spec.vocab_size
             prompt = [rng.randrange(vocab) for _ in range(prompt_len)]
+            del windows[:]
 
             def prefill_once():
                 slot = engine.acquire_slot()
@@ -406,9 +412,11 @@ def compare_designs(args) -> int:
                 "decode": {"batch": batch, "context": context, "ms_per_step": round(step_ms, 4),
                            "tok_s": round(batch / (step_ms * 1e-3)), "launches_per_step": dec.launches_per_step,
                            "frac_of_hbm": round(step_bytes / (step_ms * 1e-3) / 1e9 / pk["hbm_gbs"], 4)},
+                "clocks": clocks.summary(windows),
                 "peaks": pk["source"], "dtype": "bf16", "data": "synthetic (seeded random weights and token ids)"}))
             del llm, engine, dec
             torch.cuda.empty_cache()
+    clocks.stop()
     return 0
 
 
