@@ -400,12 +400,19 @@ def compare_designs(args) -> int:
                     dec.launch()
                 regions.append(timed(dec.launch, steps))
             step_ms = median(regions)
-            step_bytes = engine.model.parameter_bytes() + batch * (context - steps / 2) * engine.cache.kv_bytes_per_token()
+            # weights: what one token reads, plus the further experts that a batch's tokens choose
+            weight_bytes = engine.model.parameter_bytes()
+            for entry in engine.spec.schedule:
+                for part in engine.model.blocks[entry.layer].parts():
+                    if hasattr(part, "step_bytes"):
+                        weight_bytes += part.step_bytes(batch) - part.parameter_bytes()
+            step_bytes = weight_bytes + batch * (context - steps / 2) * engine.cache.kv_bytes_per_token()
             for s in slots:
                 engine.release_slot(s)
             print(json.dumps({
                 "design": name, "size": size, "width": engine.spec.hidden_size, "layers": len(engine.spec.layers),
-                "weights_read_per_step_mb": round(engine.model.parameter_bytes() / 1e6, 1),
+                "weights_read_per_token_mb": round(engine.model.parameter_bytes() / 1e6, 1),
+                "weights_read_per_decode_step_mb": round(weight_bytes / 1e6, 1),
                 "prefill": {"tokens": prompt_len, "ms": round(prefill_ms, 3), "tok_s": round(prompt_len / (prefill_ms * 1e-3)),
                             "frac_of_bf16_peak": round(flops / (prefill_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)},
                 "prefill_parts": parts,

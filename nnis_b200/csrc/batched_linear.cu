@@ -73,11 +73,32 @@ batched_rows_kernel(const T* __restrict__ A, long long lda, long long a_bs, cons
     const T* wrow = W + ((size_t)b * N + n) * K;
     const T* a = A + (size_t)b * a_bs;
     float acc[8] = {};
-    for (int k = lane; k < K; k += 32) {
-        float w = to_float(wrow[k]);
+    if (sizeof(T) == 2 && K % 8 == 0 && lda % 8 == 0 && a_bs % 8 == 0 &&
+        (((uintptr_t)A | (uintptr_t)W) & 15) == 0) {
+        // bfloat16 rows on 16-byte boundaries: eight values a load
+        for (int k = lane * 8; k < K; k += 256) {
+            uint4 wv = *reinterpret_cast<const uint4*>(wrow + k);
+            const uint32_t ws[4] = {wv.x, wv.y, wv.z, wv.w};
 #pragma unroll
-        for (int i = 0; i < 8; ++i)
-            if (m0 + i < M) acc[i] = fmaf(to_float(a[(size_t)(m0 + i) * lda + k]), w, acc[i]);
+            for (int i = 0; i < 8; ++i) {
+                if (m0 + i < M) {
+                    uint4 xv = *reinterpret_cast<const uint4*>(a + (size_t)(m0 + i) * lda + k);
+                    const uint32_t xs[4] = {xv.x, xv.y, xv.z, xv.w};
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        acc[i] = fmaf(__uint_as_float(xs[j] << 16), __uint_as_float(ws[j] << 16), acc[i]);
+                        acc[i] = fmaf(__uint_as_float(xs[j] & 0xffff0000u), __uint_as_float(ws[j] & 0xffff0000u), acc[i]);
+                    }
+                }
+            }
+        }
+    } else {
+        for (int k = lane; k < K; k += 32) {
+            float w = to_float(wrow[k]);
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+                if (m0 + i < M) acc[i] = fmaf(to_float(a[(size_t)(m0 + i) * lda + k]), w, acc[i]);
+        }
     }
 #pragma unroll
     for (int i = 0; i < 8; ++i) {

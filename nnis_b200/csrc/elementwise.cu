@@ -225,6 +225,19 @@ group_rmsnorm_kernel(const float* x, const int* __restrict__ rows,
 }
 
 // ---------------------------------------------------------------------------
+// a += b, float32, elementwise: where two branches of a layer that ran side by side meet
+// in the residual stream.
+// ---------------------------------------------------------------------------
+__global__ void add_rows_kernel(float* __restrict__ a, const float* __restrict__ b, size_t count4) {
+    pdl_wait();
+    pdl_launch_dependents();
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= count4) return;
+    float4 x = reinterpret_cast<float4*>(a)[i], y = reinterpret_cast<const float4*>(b)[i];
+    reinterpret_cast<float4*>(a)[i] = make_float4(x.x + y.x, x.y + y.y, x.z + y.z, x.w + y.w);
+}
+
+// ---------------------------------------------------------------------------
 // out[n, i] = relu(u[n, i])^2 (* sigmoid(u[n, inter]) when `gated` > 0): the
 // activation of an expert whose row of u carries, in column `inter`, the logit
 // of a gate that scales the expert's whole output.  u float32 [n, inter + gated]
@@ -433,5 +446,12 @@ NNIS_API int nnis_rope_part(const void* src, long long src_row, int src_head, in
                              len, dims);
     else
         return NNIS_ERR_UNSUPPORTED;
+    return e == cudaSuccess ? NNIS_OK : (int)e;
+}
+
+NNIS_API int nnis_add_rows(float* a, const float* b, long long count, cudaStream_t stream) {
+    if (!a || !b || count <= 0 || count % 4 || ((uintptr_t)a | (uintptr_t)b) % 16) return NNIS_ERR_ARGUMENT;
+    size_t count4 = (size_t)count / 4;
+    cudaError_t e = launch_dependent(add_rows_kernel, (unsigned)((count4 + 255) / 256), 256, 0, stream, a, b, count4);
     return e == cudaSuccess ? NNIS_OK : (int)e;
 }

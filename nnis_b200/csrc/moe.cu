@@ -17,6 +17,29 @@
 
 namespace nnis {
 
+// sum over a warp's share of two rows' product: 16-byte loads where the rows are bfloat16,
+// a multiple of eight long and 16-byte aligned, else element by element
+template <typename T>
+__device__ __forceinline__ float warp_row_dot(const T* __restrict__ a, const T* __restrict__ b, int len, int lane) {
+    float acc = 0.f;
+    if (sizeof(T) == 2 && len % 8 == 0 && (((uintptr_t)a | (uintptr_t)b) & 15) == 0) {
+        const uint4* a4 = reinterpret_cast<const uint4*>(a);
+        const uint4* b4 = reinterpret_cast<const uint4*>(b);
+        for (int i = lane; i < len / 8; i += 32) {
+            uint4 x = a4[i], y = b4[i];
+            const uint32_t xs[4] = {x.x, x.y, x.z, x.w}, ys[4] = {y.x, y.y, y.z, y.w};
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                acc = fmaf(__uint_as_float(xs[k] << 16), __uint_as_float(ys[k] << 16), acc);
+                acc = fmaf(__uint_as_float(xs[k] & 0xffff0000u), __uint_as_float(ys[k] & 0xffff0000u), acc);
+            }
+        }
+    } else {
+        for (int i = lane; i < len; i += 32) acc = fmaf(to_float(a[i]), to_float(b[i]), acc);
+    }
+    return warp_sum(acc);
+}
+
 template <typename T>
 __global__ void __launch_bounds__(256)
 moe_route_kernel(const T* __restrict__ h, const float* __restrict__ wr, const float* __restrict__ br,
@@ -95,9 +118,7 @@ moe_up_kernel(const T* __restrict__ h, const T* __restrict__ w_up, const int* __
     if (f >= ff || token_pos[n] < 0) return;
     const T* w = w_up + ((size_t)ids[pair] * ff + f) * width;
     const T* x = h + (size_t)n * width;
-    float acc = 0.f;
-    for (int i = lane; i < width; i += 32) acc = fmaf(to_float(w[i]), to_float(x[i]), acc);
-    acc = warp_sum(acc);
+    float acc = warp_row_dot(w, x, width, lane);
     if (lane == 0) {
         float a = fmaxf(acc, 0.f);
         act[(size_t)pair * ff + f] = from_float<T>(a * a);
@@ -119,9 +140,7 @@ moe_down_kernel(const T* __restrict__ act, const T* __restrict__ w_down, const i
     for (int s = 0; s < top; ++s) {
         const T* w = w_down + ((size_t)ids[n * top + s] * width + c) * ff;
         const T* a = act + ((size_t)n * top + s) * ff;
-        float acc = 0.f;
-        for (int i = lane; i < ff; i += 32) acc = fmaf(to_float(w[i]), to_float(a[i]), acc);
-        acc = warp_sum(acc);
+        float acc = warp_row_dot(w, a, ff, lane);
         sum = fmaf(weights[n * top + s], acc, sum);
     }
     if (lane == 0) residual[(size_t)n * width + c] += sum;

@@ -949,6 +949,14 @@ def group_rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, groups: int
                                      width, groups, ctypes.c_float(eps), _stream()), "group_rmsnorm")
 
 
+def add_rows(a: torch.Tensor, b: torch.Tensor) -> None:
+    """a += b, float32 of equal shape (a count of values that is a multiple of four)."""
+    _cuda(a, b)
+    _need(a.dtype == b.dtype == torch.float32 and a.shape == b.shape and a.numel() % 4 == 0,
+          "add_rows: float32 tensors of one shape, a multiple of four values")
+    _check(_lib().nnis_add_rows(_ptr(a), _ptr(b), ctypes.c_longlong(a.numel()), _stream()), "add_rows")
+
+
 def relu2_gate(u: torch.Tensor, out: torch.Tensor) -> None:
     """out = relu(u[:, :I])^2 for out [n, I]; when u has more columns than that, times
     sigmoid(u[:, I]) (the columns after the gate's are padding)."""

@@ -71,13 +71,15 @@ def main(argv=None) -> int:
     parser.add_argument("--dtype", required=True, choices=["bfloat16", "float32"])
     parser.add_argument("--out", required=True, help="folder for <step>.f32 files")
     parser.add_argument("--max-tokens", type=int, required=True,
-                        help="most tokens live requests hold at any time (each rounded up to 64)")
+                        help="most tokens live requests hold at any time")
     parser.add_argument("--device", default="cuda:0")
     args = parser.parse_args(argv)
     if args.max_tokens <= 0:
         parser.error("--max-tokens must be positive")
+    # the cache is paged: every live request may leave most of its last page of 64 unused,
+    # which a count of tokens does not include; room for 32 such pages is added
     engine = Engine.from_dir(args.model, dtype=args.dtype, device=args.device,
-                             max_tokens=args.max_tokens)
+                             max_tokens=args.max_tokens + 32 * 64)
 
     def report(step_id):
         sys.stdout.write(f"done {step_id}\n")

@@ -16,7 +16,35 @@ class Workspace:
     def __init__(self, device: torch.device):
         self.device = device
         self._buffers: Dict[Tuple[str, torch.dtype], torch.Tensor] = {}
-        self.frozen = False
+        self._frozen = False
+        self._children: Dict[str, "Workspace"] = {}
+        self._streams: Dict[str, torch.cuda.Stream] = {}
+
+    @property
+    def frozen(self) -> bool:
+        return self._frozen
+
+    @frozen.setter
+    def frozen(self, value: bool) -> None:
+        self._frozen = bool(value)
+        for child in self._children.values():
+            child.frozen = value
+
+    def child(self, name: str) -> "Workspace":
+        """Buffers of a branch of the step that runs beside the rest on a stream of its own
+        (same names, other memory); frozen together with this workspace."""
+        if name not in self._children:
+            if self._frozen:
+                raise RuntimeError(f"workspace branch {name!r} would be made after graph capture")
+            self._children[name] = Workspace(self.device)
+        return self._children[name]
+
+    def stream(self, name: str) -> torch.cuda.Stream:
+        """The stream of the branch ``name`` (made once; a captured graph forks it from and
+        joins it to the step's stream by events)."""
+        if name not in self._streams:
+            self._streams[name] = torch.cuda.Stream(device=self.device)
+        return self._streams[name]
 
     def get(self, name: str, shape, dtype: torch.dtype) -> torch.Tensor:
         count = 1
@@ -48,4 +76,5 @@ class Workspace:
         return buf[:count].view(*shape)
 
     def bytes(self) -> int:
-        return sum(b.numel() * b.element_size() for b in self._buffers.values())
+        return sum(b.numel() * b.element_size() for b in self._buffers.values()) + \
+            sum(child.bytes() for child in self._children.values())

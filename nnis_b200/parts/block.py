@@ -16,9 +16,13 @@ which norm follows, and hands what that part left to the part after it.
 """
 from __future__ import annotations
 
+import dataclasses
+import os
 from typing import Dict, Mapping, Sequence
 
 import torch
+
+from ..csrc import ops
 
 from ..weights.loader import WeightSpec
 from .base import BLOCKS, FEED_FORWARDS, MIXERS, NORMS, Part
@@ -129,7 +133,15 @@ class ParallelBlock(Block):
     """One norm, two branches that both read it: with h = norm(x),
     x += mixer(h) + ffn(h).  Roles: norm, mixer and, optionally, ffn (a layer
     without a feed-forward has none).  Both branches add into the float32 residual;
-    the feed-forward reads the normed rows, which the mixer leaves as they are."""
+    the feed-forward reads the normed rows, which the mixer leaves as they are.
+
+    In steps of single tokens the branches run side by side: such a step is a chain of
+    short kernels that wait for one another, and the two branches meet only in the residual
+    sum.  The feed-forward then runs on a stream of its own, with buffers of its own, into a
+    zeroed float32 branch buffer that one kernel adds to the residual when both are done
+    (inside a captured step the fork and the join are edges of the graph).
+    ``NNIS_PARALLEL_BRANCHES=0`` runs them one after the other."""
+    SIDE_BY_SIDE = os.environ.get("NNIS_PARALLEL_BRANCHES", "1") != "0"
 
     def __init__(self, layer_spec, dtype: torch.dtype, device: torch.device):
         super().__init__(layer_spec, dtype, device)
@@ -142,12 +154,30 @@ class ParallelBlock(Block):
 
     def forward(self, hidden: torch.Tensor, ctx, cache) -> None:
         n, width = hidden.shape
+        ws = ctx.workspace
         # (a buffer of its own: parts may use "normed" for their own rows)
-        normed = ctx.workspace.get("normed_parallel", (n, width), self.dtype)
+        normed = ws.get("normed_parallel", (n, width), self.dtype)
         ctx.emit_for = None  # the next norm reads both branches' sum: no part may begin it
         self.norm.forward(hidden, normed)
-        self.mixer.forward(normed, ctx, hidden, cache)
-        if self.ffn is not None:
+        if self.ffn is None:
+            self.mixer.forward(normed, ctx, hidden, cache)
+        elif self.SIDE_BY_SIDE and ctx.decode and width % 4 == 0:
+            main = torch.cuda.current_stream()
+            side = ws.stream("feed_forward")
+            fork, join = torch.cuda.Event(), torch.cuda.Event()
+            fork.record(main)
+            side.wait_event(fork)
+            branch_ctx = dataclasses.replace(ctx, workspace=ws.child("feed_forward"))
+            branch = branch_ctx.workspace.get("branch_sum", (n, width), torch.float32)
+            with torch.cuda.stream(side):
+                branch.zero_()
+                self.ffn.forward(normed, branch_ctx, branch)
+                join.record(side)
+            self.mixer.forward(normed, ctx, hidden, cache)
+            main.wait_event(join)
+            ops.add_rows(hidden, branch)
+        else:
+            self.mixer.forward(normed, ctx, hidden, cache)
             self.ffn.forward(normed, ctx, hidden)
 
 

@@ -87,6 +87,14 @@ class MoEFeedForward(Part):
                      if t is not None)
         return self.w_router.numel() * 4 + self.top * per_expert + shared
 
+    def step_bytes(self, rows: int) -> int:
+        """Bytes of weights that a step of ``rows`` tokens reads when the router spreads them
+        evenly: the experts that at least one token chooses (experts * (1 - (1 - top / experts)
+        ^ rows) of them in expectation), the router and the shared expert."""
+        per_expert = 2 * self.ff * self.hidden * self.w_up.element_size()
+        chosen = self.experts * (1.0 - (1.0 - self.top / self.experts) ** max(1, rows))
+        return int(self.parameter_bytes() + (chosen - self.top) * per_expert)
+
     def step_flops(self, counts, starts) -> float:
         W = self.hidden
         per_token = W * self.experts + 2 * self.top * self.ff * W + self.shared_ff * (2 * W + 1) + W
