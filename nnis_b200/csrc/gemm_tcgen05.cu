@@ -58,6 +58,13 @@ struct GemmArgs {
     bf16* v_cache;
     int nq, nkv, d, page_size;
     unsigned long long* trace;  // this launch's slot of the step's timeline, or null
+    // Grouped product (one weight matrix per group of rows): the tile of rows blockIdx.y
+    // multiplies the matrix `tile_expert[blockIdx.y]` of W = [experts, N, K] stacked along
+    // its rows (`expert_rows` = N), or does nothing where that is negative.  Null: one W.
+    // The list must be complete before the kernel ahead of this one passed its own wait
+    // (it is read ahead of this kernel's wait, with the first loads of W).
+    const int* tile_expert;
+    int expert_rows;
 };
 
 // Two CTAs share an SM when their stages leave room for it.
@@ -106,6 +113,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int m0 = blockIdx.y * kBM, n0 = blockIdx.x * BN;
+    const int expert = g.tile_expert ? g.tile_expert[blockIdx.y] : 0;
+    if (expert < 0) return;  // a tile of rows past the last group: nothing is allocated or awaited yet
+    const int w_row0 = expert * g.expert_rows + n0;  // this tile's first row of W
     const int k_slices = (g.K + kBK - 1) / kBK;
     const int k_blocks_all = (k_slices + KSUB - 1) / KSUB;
     // this CTA's run of k-blocks (all of them without a split of K)
@@ -153,7 +163,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                             &full_bar[s]);
             } else {
                 unsigned char* b_dst = tile_b + (size_t)s * kStageB + (size_t)h * NB * kBytesB;
-                tma_load_2d(b_dst, &map_w, k0, n0, &full_bar[s]);
+                tma_load_2d(b_dst, &map_w, k0, w_row0, &full_bar[s]);
                 if (NB == 2) tma_load_2d(b_dst + kBytesB, &map_w, k0, inter + n0, &full_bar[s]);
             }
         }
@@ -591,6 +601,7 @@ NNIS_API int nnis_gemm_tc(const void* A, const void* W, const float* bias, void*
     g.table_cols = table_cols; g.cos_t = cos_t; g.sin_t = sin_t; g.k_cache = (bf16*)k_cache;
     g.v_cache = (bf16*)v_cache; g.nq = nq; g.nkv = nkv; g.d = d; g.page_size = page_size;
     g.k_splits = 1; g.split_scratch = nullptr; g.split_tickets = nullptr;
+    g.tile_expert = nullptr; g.expert_rows = 0;
     static const char* const kNames[] = {"gemm store", "gemm store_f32", "gemm add_f32", "gemm gated", "gemm qkv"};
     g.trace = trace_slot(mode >= 0 && mode <= 4 ? kNames[mode] : "gemm");
     int sms = sm_count > 0 ? sm_count : 148;
@@ -653,4 +664,37 @@ NNIS_API int nnis_gemm_tc(const void* A, const void* W, const float* bias, void*
 #undef NNIS_GEMM_TC64
 #undef NNIS_GEMM_TC128
 #undef NNIS_GEMM_TC
+}
+
+// Grouped product on the tensor cores: C[M, N] (float32) = A[M, K] . W[tile_expert[m / 128]]^T
+// with W = [experts, N, K] bfloat16 and A's rows sorted by expert in runs padded to 128 rows
+// (`tile_expert` int32 [ceil(M / 128)], negative past the last run: those tiles are left
+// alone).  The tcgen05 kernel of nnis_gemm_tc with one more coordinate for W.  Refuses
+// (NNIS_ERR_UNSUPPORTED) K not a multiple of 8 or N not a multiple of 4.
+NNIS_API int nnis_gemm_tc_grouped(const void* A, const void* W, void* C, int M, int N, int K, int experts,
+                                  const int* tile_expert, int sm_count, int* status, int pdl,
+                                  cudaStream_t stream) {
+    using namespace nnis;
+    if (M <= 0 || N <= 0 || K <= 0 || experts <= 0 || !A || !W || !C || !tile_expert) return NNIS_ERR_ARGUMENT;
+    if (K % 8 || N % 4 || (long long)experts * N > 0x7fffffffLL) return NNIS_ERR_UNSUPPORTED;
+    if (((uintptr_t)A | (uintptr_t)W | (uintptr_t)C) % 16) return NNIS_ERR_ALIGNMENT;
+    if ((M + kBM - 1) / kBM > 65535) return NNIS_ERR_UNSUPPORTED;
+    GemmArgs g = {};
+    g.out = C; g.M = M; g.N = N; g.K = K; g.status = status; g.k_splits = 1;
+    g.tile_expert = tile_expert; g.expert_rows = N;
+    g.trace = trace_slot("gemm grouped");
+    const int sms = sm_count > 0 ? sm_count : 148;
+    const long m_tiles = (M + kBM - 1) / kBM;
+    const long tiles128 = (long)((N + 127) / 128) * m_tiles;
+    const bool wide = tiles128 >= sms;
+    CUtensorMap ma, mw, mo;
+    if (!make_map(&ma, A, M, K, kBM) || !make_map(&mw, W, (long long)experts * N, K, wide ? 128 : 64) ||
+        !make_map(&mo, C, M, N, kBM, 0, 4))
+        return NNIS_ERR_UNSUPPORTED;
+    g.out_by_tma = 1;
+    if (wide)
+        return tiles128 <= sms ? launch_gemm_tc<128, 3, GEMM_STORE_F32, 2>(ma, mw, mo, g, pdl != 0, stream)
+                               : launch_gemm_tc<128, 3, GEMM_STORE_F32, 1>(ma, mw, mo, g, pdl != 0, stream);
+    return m_tiles * ((N + 63) / 64) <= sms ? launch_gemm_tc<64, 2, GEMM_STORE_F32, 4>(ma, mw, mo, g, pdl != 0, stream)
+                                            : launch_gemm_tc<64, 2, GEMM_STORE_F32, 2>(ma, mw, mo, g, pdl != 0, stream);
 }

@@ -21,7 +21,7 @@ namespace nnis {
 constexpr int kGroupRows = 64;
 
 __global__ void __launch_bounds__(1024)
-moe_sort_kernel(const int* __restrict__ ids, int n_pairs, int experts, int max_tiles,
+moe_sort_kernel(const int* __restrict__ ids, int n_pairs, int experts, int max_tiles, int tile_rows,
                 int* __restrict__ perm, int* __restrict__ place, int* __restrict__ tile_expert) {
     extern __shared__ int sort_smem[];
     int* count = sort_smem;             // [experts]
@@ -29,7 +29,7 @@ moe_sort_kernel(const int* __restrict__ ids, int n_pairs, int experts, int max_t
     int* cursor = first + experts + 1;  // [experts]
     const int tid = threadIdx.x;
     for (int e = tid; e < experts; e += 1024) count[e] = cursor[e] = 0;
-    for (int p = tid; p < max_tiles * kGroupRows; p += 1024) perm[p] = -1;
+    for (int p = tid; p < max_tiles * tile_rows; p += 1024) perm[p] = -1;
     __syncthreads();
     for (int p = tid; p < n_pairs; p += 1024) atomicAdd(&count[ids[p]], 1);
     __syncthreads();
@@ -37,13 +37,13 @@ moe_sort_kernel(const int* __restrict__ ids, int n_pairs, int experts, int max_t
         int at = 0;
         for (int e = 0; e < experts; ++e) {
             first[e] = at;
-            at += (count[e] + kGroupRows - 1) / kGroupRows * kGroupRows;
+            at += (count[e] + tile_rows - 1) / tile_rows * tile_rows;
         }
         first[experts] = at;
     }
     __syncthreads();
     for (int t = tid; t < max_tiles; t += 1024) {
-        int row = t * kGroupRows, found = -1;
+        int row = t * tile_rows, found = -1;
         if (row < first[experts]) {
             int lo = 0, hi = experts - 1;  // the last expert whose run starts at or before the row
             while (lo < hi) {
@@ -166,6 +166,20 @@ grouped_mma_kernel(const bf16* __restrict__ a, int lda, const int* __restrict__ 
     }
 }
 
+// x_sorted[place] = x[perm[place] / top] (zeros where perm is negative): the rows of the
+// first grouped product in the sorted order, for the kernel that takes its rows by TMA
+__global__ void __launch_bounds__(256)
+moe_gather_kernel(const bf16* __restrict__ x, const int* __restrict__ perm, int top,
+                  bf16* __restrict__ x_sorted, int width) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const long long at = blockIdx.x;
+    const int p = perm[at];
+    const uint4* src = reinterpret_cast<const uint4*>(x + (size_t)(p < 0 ? 0 : p / top) * width);
+    uint4* dst = reinterpret_cast<uint4*>(x_sorted + (size_t)at * width);
+    for (int c = threadIdx.x; c < width / 8; c += 256) dst[c] = p < 0 ? make_uint4(0, 0, 0, 0) : src[c];
+}
+
 __global__ void __launch_bounds__(256)
 moe_combine_kernel(const float* __restrict__ y, const int* __restrict__ place,
                    const float* __restrict__ weights, float* __restrict__ residual, int width, int top) {
@@ -244,8 +258,8 @@ NNIS_API int nnis_moe_grouped(const void* x, const void* w_up, const void* w_dow
     if (((uintptr_t)x | (uintptr_t)w_up | (uintptr_t)w_down | (uintptr_t)act) % 16) return NNIS_ERR_ALIGNMENT;
     const long long pairs = (long long)n_tokens * top;
     const int tiles = nnis_moe_grouped_tiles(pairs, experts);
-    moe_sort_kernel<<<1, 1024, (3 * experts + 1) * sizeof(int), stream>>>(ids, (int)pairs, experts, tiles, perm,
-                                                                         place, tile_expert);
+    moe_sort_kernel<<<1, 1024, (3 * experts + 1) * sizeof(int), stream>>>(ids, (int)pairs, experts, tiles,
+                                                                         kGroupRows, perm, place, tile_expert);
     const size_t smem = kGroupedSmem;
     int code = configure_grouped();
     if (code != NNIS_OK) return code;
@@ -253,6 +267,49 @@ NNIS_API int nnis_moe_grouped(const void* x, const void* w_up, const void* w_dow
         (const bf16*)x, width, perm, top, (const bf16*)w_up, tile_expert, act, ff, width, 0, 0, 0, 0);
     grouped_mma_kernel<1><<<dim3(tiles, (width + 63) / 64), 128, smem, stream>>>(
         (const bf16*)act, ff, perm, top, (const bf16*)w_down, tile_expert, y, width, ff, 0, 0, 0, 0);
+    moe_combine_kernel<<<n_tokens, 256, 0, stream>>>(y, place, weights, residual, width, top);
+    NNIS_RETURN_LAUNCH();
+}
+
+// The same with both products on the tcgen05 kernel (nnis_gemm_tc_grouped): runs padded to
+// 128 rows, the first product's rows gathered into x_sorted [tiles * 128, width] first, its
+// float32 output u [tiles * 128, ff] squared (relu) into act by the activation kernel.
+// tiles = nnis_moe_grouped_tiles_tc(n_tokens * top, experts); scratch as nnis_moe_grouped with
+// 128 rows a tile, plus x_sorted (bfloat16) and u (float32).
+NNIS_API int nnis_moe_grouped_tiles_tc(long long n_pairs, int experts) {
+    return (int)((n_pairs + 127) / 128) + experts;
+}
+
+extern "C" int nnis_gemm_tc_grouped(const void* A, const void* W, void* C, int M, int N, int K, int experts,
+                                    const int* tile_expert, int sm_count, int* status, int pdl,
+                                    cudaStream_t stream);
+extern "C" int nnis_relu2_gate(const float* u, void* out, int out_dtype, long long n_rows, int inter, int gated,
+                               cudaStream_t stream);
+
+NNIS_API int nnis_moe_grouped_tc(const void* x, const void* w_up, const void* w_down, const int* ids,
+                                 const float* weights, int* perm, int* place, int* tile_expert, void* x_sorted,
+                                 float* u, void* act, float* y, float* residual, int n_tokens, int width, int ff,
+                                 int experts, int top, int sm_count, int* status, int pdl, cudaStream_t stream) {
+    if (n_tokens <= 0 || top <= 0 || !x || !w_up || !w_down || !ids || !weights || !perm || !place ||
+        !tile_expert || !x_sorted || !u || !act || !y || !residual)
+        return NNIS_ERR_ARGUMENT;
+    if (!nnis_moe_grouped_takes(width, ff, experts)) return NNIS_ERR_UNSUPPORTED;
+    if (((uintptr_t)x | (uintptr_t)x_sorted) % 16) return NNIS_ERR_ALIGNMENT;
+    const long long pairs = (long long)n_tokens * top;
+    const int tiles = nnis_moe_grouped_tiles_tc(pairs, experts);
+    const int rows = tiles * 128;
+    moe_sort_kernel<<<1, 1024, (3 * experts + 1) * sizeof(int), stream>>>(ids, (int)pairs, experts, tiles, 128, perm,
+                                                                         place, tile_expert);
+    cudaError_t e = launch_dependent(moe_gather_kernel, (unsigned)rows, 256, 0, stream, (const bf16*)x,
+                                     (const int*)perm, top, (bf16*)x_sorted, width);
+    if (e != cudaSuccess) return (int)e;
+    int code = nnis_gemm_tc_grouped(x_sorted, w_up, u, rows, ff, width, experts, tile_expert, sm_count, status, pdl,
+                                    stream);
+    if (code != NNIS_OK) return code;
+    code = nnis_relu2_gate(u, act, NNIS_DTYPE_BF16, rows, ff, 0, stream);
+    if (code != NNIS_OK) return code;
+    code = nnis_gemm_tc_grouped(act, w_down, y, rows, width, ff, experts, tile_expert, sm_count, status, pdl, stream);
+    if (code != NNIS_OK) return code;
     moe_combine_kernel<<<n_tokens, 256, 0, stream>>>(y, place, weights, residual, width, top);
     NNIS_RETURN_LAUNCH();
 }

@@ -32,6 +32,7 @@ from .linear import ADD_F32, STORE_F32, linear
 
 class MoEFeedForward(Part):
     GROUPED_FROM = 32  # tokens of a prompt step from which the pairs are sorted by expert
+    TCGEN05_ROWS = 96  # (token, expert) pairs an expert on average from which runs are padded to 128 rows
 
     def __init__(self, params, prefix, dtype, device):
         super().__init__(params, prefix, dtype, device)
@@ -106,9 +107,22 @@ class MoEFeedForward(Part):
         ids = ws.get("moe_ids", (n, self.top), torch.int32)
         weights = ws.get("moe_weights", (n, self.top), torch.float32)
         ops.moe_route(x, self.w_router, self.b_router, ctx.token_pos, ids, weights, self.top)
-        if self.dtype == torch.bfloat16 and not ctx.decode and n >= self.GROUPED_FROM \
-                and ops.moe_grouped_takes(self.hidden, self.ff, self.experts):
-            # many tokens: pairs sorted by expert, grouped products on the tensor cores
+        grouped = self.dtype == torch.bfloat16 and not ctx.decode and n >= self.GROUPED_FROM \
+            and ops.moe_grouped_takes(self.hidden, self.ff, self.experts)
+        if grouped and ops.TC_GEMM and n * self.top >= self.TCGEN05_ROWS * self.experts:
+            # many tokens an expert: runs padded to 128 rows, both products on the tcgen05 kernel
+            tiles = ops.moe_grouped_tc_tiles(n * self.top, self.experts)
+            ops.moe_grouped_tc(x, self.w_up, self.w_down, ids, weights,
+                               ws.get("moe_perm", (tiles * 128,), torch.int32),
+                               ws.get("moe_place", (n * self.top,), torch.int32),
+                               ws.get("moe_tile_expert", (tiles,), torch.int32),
+                               ws.get("moe_x_sorted", (tiles * 128, self.hidden), self.dtype),
+                               ws.get("moe_up_sorted", (tiles * 128, self.ff), torch.float32),
+                               ws.get("moe_act_sorted", (tiles * 128, self.ff), self.dtype),
+                               ws.get("moe_y_sorted", (tiles * 128, self.hidden), torch.float32), residual,
+                               self.top)
+        elif grouped:
+            # pairs sorted by expert in runs padded to 64 rows, grouped products on mma.sync tiles
             tiles = ops.moe_grouped_tiles(n * self.top, self.experts)
             ops.moe_grouped(x, self.w_up, self.w_down, ids, weights,
                             ws.get("moe_perm", (tiles * 64,), torch.int32),

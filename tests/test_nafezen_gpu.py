@@ -165,7 +165,8 @@ def test_each_mechanism_alone(models, name, dtype, tmp_path):
     rng = random.Random(11)
     vocab = read_config(models[name])["vocab"]
     sequences, trace = {}, TraceBuilder()
-    for i, n in enumerate((1, 2, 3, 64, 65, 131)):  # the first tokens, a page's border
+    # the first tokens, a page's border, and enough tokens an expert for the runs of 128 rows
+    for i, n in enumerate((1, 2, 3, 64, 65, 131, 300)):
         sequences[f"w{i}"] = random_tokens(rng, n, vocab)
         trace.step([(f"w{i}", sequences[f"w{i}"], range(n))], end=[f"w{i}"])
     toks = sequences["d"] = random_tokens(rng, 75, vocab)  # decoding from the second token on
