@@ -65,6 +65,7 @@ struct GemmArgs {
     // (it is read ahead of this kernel's wait, with the first loads of W).
     const int* tile_expert;
     int expert_rows;
+    int square_relu;  // the epilogue stores relu(x)^2 (the experts' activation) instead of x
 };
 
 // Two CTAs share an SM when their stages leave room for it.
@@ -452,6 +453,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 #pragma unroll
                     for (int i = 0; i < 32; ++i)
                         f[i] = __uint_as_float(v[i]) + ((g.bias && nb + i < g.N) ? g.bias[nb + i] : 0.f);
+                    if (g.square_relu) {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) {
+                            float a = fmaxf(f[i], 0.f);
+                            f[i] = a * a;
+                        }
+                    }
                 }
                 if (g.out_by_tma) {
                     unsigned char* box = stage_row + (size_t)(c0 / kBoxCols) * (kBM * 128);
@@ -601,7 +609,7 @@ NNIS_API int nnis_gemm_tc(const void* A, const void* W, const float* bias, void*
     g.table_cols = table_cols; g.cos_t = cos_t; g.sin_t = sin_t; g.k_cache = (bf16*)k_cache;
     g.v_cache = (bf16*)v_cache; g.nq = nq; g.nkv = nkv; g.d = d; g.page_size = page_size;
     g.k_splits = 1; g.split_scratch = nullptr; g.split_tickets = nullptr;
-    g.tile_expert = nullptr; g.expert_rows = 0;
+    g.tile_expert = nullptr; g.expert_rows = 0; g.square_relu = 0;
     static const char* const kNames[] = {"gemm store", "gemm store_f32", "gemm add_f32", "gemm gated", "gemm qkv"};
     g.trace = trace_slot(mode >= 0 && mode <= 4 ? kNames[mode] : "gemm");
     int sms = sm_count > 0 ? sm_count : 148;
@@ -666,22 +674,23 @@ NNIS_API int nnis_gemm_tc(const void* A, const void* W, const float* bias, void*
 #undef NNIS_GEMM_TC
 }
 
-// Grouped product on the tensor cores: C[M, N] (float32) = A[M, K] . W[tile_expert[m / 128]]^T
-// with W = [experts, N, K] bfloat16 and A's rows sorted by expert in runs padded to 128 rows
+// Grouped product on the tensor cores: C[M, N] = A[M, K] . W[tile_expert[m / 128]]^T with
+// W = [experts, N, K] bfloat16 and A's rows sorted by expert in runs padded to 128 rows
 // (`tile_expert` int32 [ceil(M / 128)], negative past the last run: those tiles are left
-// alone).  The tcgen05 kernel of nnis_gemm_tc with one more coordinate for W.  Refuses
-// (NNIS_ERR_UNSUPPORTED) K not a multiple of 8 or N not a multiple of 4.
+// alone).  The tcgen05 kernel of nnis_gemm_tc with one more coordinate for W.  `square_relu`:
+// C is bfloat16 and holds relu(.)^2; else C is float32.  Refuses (NNIS_ERR_UNSUPPORTED) K or
+// (bfloat16 C) N not a multiple of 8, (float32 C) N not a multiple of 4.
 NNIS_API int nnis_gemm_tc_grouped(const void* A, const void* W, void* C, int M, int N, int K, int experts,
-                                  const int* tile_expert, int sm_count, int* status, int pdl,
+                                  const int* tile_expert, int square_relu, int sm_count, int* status, int pdl,
                                   cudaStream_t stream) {
     using namespace nnis;
     if (M <= 0 || N <= 0 || K <= 0 || experts <= 0 || !A || !W || !C || !tile_expert) return NNIS_ERR_ARGUMENT;
-    if (K % 8 || N % 4 || (long long)experts * N > 0x7fffffffLL) return NNIS_ERR_UNSUPPORTED;
+    if (K % 8 || N % (square_relu ? 8 : 4) || (long long)experts * N > 0x7fffffffLL) return NNIS_ERR_UNSUPPORTED;
     if (((uintptr_t)A | (uintptr_t)W | (uintptr_t)C) % 16) return NNIS_ERR_ALIGNMENT;
     if ((M + kBM - 1) / kBM > 65535) return NNIS_ERR_UNSUPPORTED;
     GemmArgs g = {};
     g.out = C; g.M = M; g.N = N; g.K = K; g.status = status; g.k_splits = 1;
-    g.tile_expert = tile_expert; g.expert_rows = N;
+    g.tile_expert = tile_expert; g.expert_rows = N; g.square_relu = square_relu ? 1 : 0;
     g.trace = trace_slot("gemm grouped");
     const int sms = sm_count > 0 ? sm_count : 148;
     const long m_tiles = (M + kBM - 1) / kBM;
@@ -689,12 +698,17 @@ NNIS_API int nnis_gemm_tc_grouped(const void* A, const void* W, void* C, int M, 
     const bool wide = tiles128 >= sms;
     CUtensorMap ma, mw, mo;
     if (!make_map(&ma, A, M, K, kBM) || !make_map(&mw, W, (long long)experts * N, K, wide ? 128 : 64) ||
-        !make_map(&mo, C, M, N, kBM, 0, 4))
+        !(square_relu ? make_map(&mo, C, M, N, kBM) : make_map(&mo, C, M, N, kBM, 0, 4)))
         return NNIS_ERR_UNSUPPORTED;
     g.out_by_tma = 1;
-    if (wide)
-        return tiles128 <= sms ? launch_gemm_tc<128, 3, GEMM_STORE_F32, 2>(ma, mw, mo, g, pdl != 0, stream)
-                               : launch_gemm_tc<128, 3, GEMM_STORE_F32, 1>(ma, mw, mo, g, pdl != 0, stream);
-    return m_tiles * ((N + 63) / 64) <= sms ? launch_gemm_tc<64, 2, GEMM_STORE_F32, 4>(ma, mw, mo, g, pdl != 0, stream)
-                                            : launch_gemm_tc<64, 2, GEMM_STORE_F32, 2>(ma, mw, mo, g, pdl != 0, stream);
+    const long tiles64 = m_tiles * ((N + 63) / 64);
+#define NNIS_GROUPED(MODE) \
+    if (wide) \
+        return tiles128 <= sms ? launch_gemm_tc<128, 3, MODE, 2>(ma, mw, mo, g, pdl != 0, stream) \
+                               : launch_gemm_tc<128, 3, MODE, 1>(ma, mw, mo, g, pdl != 0, stream); \
+    return tiles64 <= sms ? launch_gemm_tc<64, 2, MODE, 4>(ma, mw, mo, g, pdl != 0, stream) \
+                          : launch_gemm_tc<64, 2, MODE, 2>(ma, mw, mo, g, pdl != 0, stream)
+    if (square_relu) { NNIS_GROUPED(GEMM_STORE); }
+    NNIS_GROUPED(GEMM_STORE_F32);
+#undef NNIS_GROUPED
 }

@@ -272,26 +272,23 @@ NNIS_API int nnis_moe_grouped(const void* x, const void* w_up, const void* w_dow
 }
 
 // The same with both products on the tcgen05 kernel (nnis_gemm_tc_grouped): runs padded to
-// 128 rows, the first product's rows gathered into x_sorted [tiles * 128, width] first, its
-// float32 output u [tiles * 128, ff] squared (relu) into act by the activation kernel.
-// tiles = nnis_moe_grouped_tiles_tc(n_tokens * top, experts); scratch as nnis_moe_grouped with
-// 128 rows a tile, plus x_sorted (bfloat16) and u (float32).
+// 128 rows, the first product's rows gathered into x_sorted [tiles * 128, width] first, relu^2
+// in that product's epilogue.  tiles = nnis_moe_grouped_tiles_tc(n_tokens * top, experts);
+// scratch as nnis_moe_grouped with 128 rows a tile, plus x_sorted (bfloat16).
 NNIS_API int nnis_moe_grouped_tiles_tc(long long n_pairs, int experts) {
     return (int)((n_pairs + 127) / 128) + experts;
 }
 
 extern "C" int nnis_gemm_tc_grouped(const void* A, const void* W, void* C, int M, int N, int K, int experts,
-                                    const int* tile_expert, int sm_count, int* status, int pdl,
+                                    const int* tile_expert, int square_relu, int sm_count, int* status, int pdl,
                                     cudaStream_t stream);
-extern "C" int nnis_relu2_gate(const float* u, void* out, int out_dtype, long long n_rows, int inter, int gated,
-                               cudaStream_t stream);
 
 NNIS_API int nnis_moe_grouped_tc(const void* x, const void* w_up, const void* w_down, const int* ids,
                                  const float* weights, int* perm, int* place, int* tile_expert, void* x_sorted,
-                                 float* u, void* act, float* y, float* residual, int n_tokens, int width, int ff,
+                                 void* act, float* y, float* residual, int n_tokens, int width, int ff,
                                  int experts, int top, int sm_count, int* status, int pdl, cudaStream_t stream) {
     if (n_tokens <= 0 || top <= 0 || !x || !w_up || !w_down || !ids || !weights || !perm || !place ||
-        !tile_expert || !x_sorted || !u || !act || !y || !residual)
+        !tile_expert || !x_sorted || !act || !y || !residual)
         return NNIS_ERR_ARGUMENT;
     if (!nnis_moe_grouped_takes(width, ff, experts)) return NNIS_ERR_UNSUPPORTED;
     if (((uintptr_t)x | (uintptr_t)x_sorted) % 16) return NNIS_ERR_ALIGNMENT;
@@ -303,12 +300,11 @@ NNIS_API int nnis_moe_grouped_tc(const void* x, const void* w_up, const void* w_
     cudaError_t e = launch_dependent(moe_gather_kernel, (unsigned)rows, 256, 0, stream, (const bf16*)x,
                                      (const int*)perm, top, (bf16*)x_sorted, width);
     if (e != cudaSuccess) return (int)e;
-    int code = nnis_gemm_tc_grouped(x_sorted, w_up, u, rows, ff, width, experts, tile_expert, sm_count, status, pdl,
-                                    stream);
+    int code = nnis_gemm_tc_grouped(x_sorted, w_up, act, rows, ff, width, experts, tile_expert, 1, sm_count, status,
+                                    pdl, stream);
     if (code != NNIS_OK) return code;
-    code = nnis_relu2_gate(u, act, NNIS_DTYPE_BF16, rows, ff, 0, stream);
-    if (code != NNIS_OK) return code;
-    code = nnis_gemm_tc_grouped(act, w_down, y, rows, width, ff, experts, tile_expert, sm_count, status, pdl, stream);
+    code = nnis_gemm_tc_grouped(act, w_down, y, rows, width, ff, experts, tile_expert, 0, sm_count, status, pdl,
+                                stream);
     if (code != NNIS_OK) return code;
     moe_combine_kernel<<<n_tokens, 256, 0, stream>>>(y, place, weights, residual, width, top);
     NNIS_RETURN_LAUNCH();

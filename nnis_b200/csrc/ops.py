@@ -1238,12 +1238,12 @@ def moe_grouped_tc_tiles(n_pairs: int, experts: int) -> int:
 
 def moe_grouped_tc(h: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor, ids: torch.Tensor,
                    weights: torch.Tensor, perm: torch.Tensor, place: torch.Tensor, tile_expert: torch.Tensor,
-                   x_sorted: torch.Tensor, u: torch.Tensor, act: torch.Tensor, y: torch.Tensor,
+                   x_sorted: torch.Tensor, act: torch.Tensor, y: torch.Tensor,
                    residual: torch.Tensor, top: int) -> None:
     """``moe_grouped`` with both products on the tcgen05 kernel: runs padded to tiles of 128
     rows (``moe_grouped_tc_tiles``), the rows gathered into ``x_sorted`` [tiles * 128, width]
-    first, the first product's float32 output ``u`` [tiles * 128, ff] squared into ``act``."""
-    _cuda(h, w_up, w_down, ids, weights, perm, place, tile_expert, x_sorted, u, act, y, residual)
+    first, relu^2 in the first product's epilogue."""
+    _cuda(h, w_up, w_down, ids, weights, perm, place, tile_expert, x_sorted, act, y, residual)
     n, width = h.shape
     experts, ff, _ = w_up.shape
     rows = moe_grouped_tc_tiles(n * top, experts) * 128
@@ -1254,10 +1254,10 @@ def moe_grouped_tc(h: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor, id
     _need(moe_grouped_takes(width, ff, experts) and TC_GEMM, "moe_grouped_tc: sizes not taken")
     _need(perm.dtype == place.dtype == tile_expert.dtype == ids.dtype == torch.int32 and perm.numel() >= rows
           and place.numel() >= n * top and tile_expert.numel() >= rows // 128, "moe_grouped_tc: int32 scratch")
-    _need(x_sorted.numel() >= rows * width and act.numel() >= rows * ff and u.dtype == y.dtype == torch.float32
-          and u.numel() >= rows * ff and y.numel() >= rows * width, "moe_grouped_tc: scratch")
+    _need(x_sorted.numel() >= rows * width and act.numel() >= rows * ff and y.dtype == torch.float32
+          and y.numel() >= rows * width, "moe_grouped_tc: scratch")
     _need(residual.dtype == torch.float32 and tuple(residual.shape) == (n, width), "moe_grouped_tc: residual")
     _check(_lib().nnis_moe_grouped_tc(_ptr(h), _ptr(w_up), _ptr(w_down), _ptr(ids), _ptr(weights), _ptr(perm),
-                                      _ptr(place), _ptr(tile_expert), _ptr(x_sorted), _ptr(u), _ptr(act), _ptr(y),
+                                      _ptr(place), _ptr(tile_expert), _ptr(x_sorted), _ptr(act), _ptr(y),
                                       _ptr(residual), n, width, ff, experts, top, sm_count(h.device),
-                                      _ptr(status_word(h.device)), PDL, _stream()), "moe_grouped_tc", 6)
+                                      _ptr(status_word(h.device)), PDL, _stream()), "moe_grouped_tc", 5)

@@ -117,7 +117,6 @@ class MoEFeedForward(Part):
                                ws.get("moe_place", (n * self.top,), torch.int32),
                                ws.get("moe_tile_expert", (tiles,), torch.int32),
                                ws.get("moe_x_sorted", (tiles * 128, self.hidden), self.dtype),
-                               ws.get("moe_up_sorted", (tiles * 128, self.ff), torch.float32),
                                ws.get("moe_act_sorted", (tiles * 128, self.ff), self.dtype),
                                ws.get("moe_y_sorted", (tiles * 128, self.hidden), torch.float32), residual,
                                self.top)
