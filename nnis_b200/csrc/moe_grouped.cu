@@ -12,6 +12,11 @@
 //                 second reads the sorted activations and stores float32.
 //   moe_combine   residual[n] += sum_s weight[n, s] * y[place[n, s]], in the router's order
 //
+// Where an expert gets many rows (nnis_moe_grouped_tc) the runs are padded to 128 rows
+// instead, moe_gather puts the tokens' inputs into the sorted order, and both products run
+// on the tcgen05 kernel of the dense projections with one weight matrix per tile of rows
+// (gemm_tcgen05.cu: nnis_gemm_tc_grouped), relu^2 in the first one's epilogue.
+//
 // A row's result depends on nothing but the row, so the order inside an expert's run
 // (which the sort's atomics decide) changes no bit of the output.
 #include "mma_helpers.cuh"

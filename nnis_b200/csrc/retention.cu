@@ -10,6 +10,8 @@
 //                    of the state tile in registers.  Steps of single tokens.
 //   retention_chunk  prompts and later chunks of them (the state says where a sequence
 //                    stands): 32 tokens at a time, see below.
+//   retention_prefix, retention_carry   long prompts cut into runs that are worked side by
+//                    side: the states between the runs, and what they give each token.
 //   retention_gate   o / rms(o) per head, times silu(g), rounded once.
 //
 // Packed input rows: [q (H dim) | k (H dim) | v (H vdim) | g (H vdim)].

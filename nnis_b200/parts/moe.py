@@ -12,7 +12,9 @@ applied to the activation, before the down-projection adds into the residual.
 The experts' matrices are stacked ([experts, ff, width] and [experts, width, ff]) so
 that one kernel serves all of them from the router's ids.  Steps of few tokens run a
 product per (token, chosen expert); prompt steps in bfloat16 sort the pairs by expert and
-run two grouped products on the tensor cores.
+run two grouped products on the tensor cores: the tcgen05 kernel of the dense projections
+with one weight matrix per tile of 128 rows where an expert gets many rows, 64 x 64
+mma.sync tiles where it gets few.
 
 params: hidden_size, experts, top, ff, shared_ff (0: no shared expert), activation
 ("relu2"), names {router, router_bias, expert (a format with {e}), up, down,
