@@ -11,9 +11,12 @@ Each schedule entry of a model may ask for one of two things:
   wholly out of the window.
   With ``values=False`` the group keeps one tensor only (``v`` is None): rows that
   serve as keys and carry the values inside them, as latent attention's do.
+  ``value_dim`` gives the values a size of their own (0: the keys' size).
 * ``StateRequest`` - a fixed-size tensor per sequence, ``[slots, *shape]``,
   zeroed when a slot is taken: the state of a recurrent mixer (retention's
-  ``[heads, dim, vdim]`` in float32).
+  ``[heads, dim, vdim]`` in float32).  ``extra`` lists further tensors of the same
+  kind ((shape, dtype) each) for a mixer whose state has several parts (a recurrence's
+  sums and the last inputs of a short convolution, say).
 
 Lengths are per slot (all layers advance together inside a step).  Positions at
 or beyond a slot's length are never read, so a reused slot cannot see what its
@@ -38,12 +41,14 @@ class KVRequest:
     head_dim: int
     window: int = 0
     values: bool = True  # False: no storage for values (the key rows carry them)
+    value_dim: int = 0  # size of a value head; 0: head_dim
 
 
 @dataclass(frozen=True)
 class StateRequest:
     shape: Tuple[int, ...]
     dtype: torch.dtype = torch.float32
+    extra: Tuple[Tuple[Tuple[int, ...], torch.dtype], ...] = ()  # further state tensors
 
 
 @dataclass
@@ -61,7 +66,7 @@ class KVView:
     """What an attention-like part gets: its own layer of a group's storage."""
     group: int
     k: torch.Tensor  # [pages, kv_heads, page_size, head_dim]
-    v: Optional[torch.Tensor]  # None for a group without storage for values
+    v: Optional[torch.Tensor]  # [pages, kv_heads, page_size, value_dim]; None for a group without values
     page_size: int
     window: int
     ahead: int = 0  # elements from k (and v) to those of the group's layer that runs next; 0: none
@@ -70,17 +75,18 @@ class KVView:
 @dataclass
 class StateView:
     state: torch.Tensor  # [slots, *shape]
+    extra: Tuple[torch.Tensor, ...] = ()  # [slots, *shape] of every further tensor asked for
 
 
 class _KVGroup:
-    def __init__(self, key: Tuple[int, int, int, bool], entries: List[int], pages: int,
+    def __init__(self, key: Tuple[int, int, int, bool, int], entries: List[int], pages: int,
                  dtype: torch.dtype, device: torch.device):
-        self.kv_heads, self.head_dim, self.window, self.values = key
+        self.kv_heads, self.head_dim, self.window, self.values, self.value_dim = key
         self.entries = entries
         self.pool = FreeList(pages, "page")
         shape = (len(entries), pages, self.kv_heads, PAGE_SIZE, self.head_dim)
         self.k = torch.zeros(shape, dtype=dtype, device=device)
-        self.v = torch.zeros(shape, dtype=dtype, device=device) if self.values else None
+        self.v = torch.zeros((*shape[:4], self.value_dim), dtype=dtype, device=device) if self.values else None
         # per slot: logical page index -> page id, -1 where given back
         self.tables: Dict[int, List[int]] = {}
 
@@ -112,10 +118,11 @@ class CacheManager:
         self.owners: List[int] = [0] * max_slots  # how many sequences have held each slot
         self.groups: List[_KVGroup] = []
         self._views: List[Optional[Union[KVView, StateView]]] = []
-        by_key: Dict[Tuple[int, int, int, bool], List[int]] = {}
+        by_key: Dict[Tuple[int, int, int, bool, int], List[int]] = {}
         for i, r in enumerate(requests):
             if isinstance(r, KVRequest):
-                by_key.setdefault((r.kv_heads, r.head_dim, r.window, bool(r.values)), []).append(i)
+                by_key.setdefault((r.kv_heads, r.head_dim, r.window, bool(r.values),
+                                   (r.value_dim or r.head_dim) if r.values else 0), []).append(i)
         group_of: Dict[int, Tuple[int, int]] = {}
         for key, entries in by_key.items():
             g = _KVGroup(key, entries, self.pages_total, dtype, self.device)
@@ -131,9 +138,10 @@ class CacheManager:
                 self._views.append(KVView(gi, g.k[j], g.v[j] if g.values else None, PAGE_SIZE, g.window,
                                           (nxt - j) * g.k[0].numel()))
             elif isinstance(r, StateRequest):
-                t = torch.zeros((max_slots, *r.shape), dtype=r.dtype, device=self.device)
-                self._states.append(t)
-                self._views.append(StateView(t))
+                made = [torch.zeros((max_slots, *shape), dtype=dtype, device=self.device)
+                        for shape, dtype in ((r.shape, r.dtype), *r.extra)]
+                self._states.extend(made)
+                self._views.append(StateView(made[0], tuple(made[1:])))
             elif r is None:
                 self._views.append(None)
             else:
@@ -282,7 +290,7 @@ class CacheManager:
     def kv_bytes_per_token(self) -> int:
         """Bytes of keys and values that one position of one sequence holds over all
         layers (a windowed group counted like a full one)."""
-        return sum((2 if g.values else 1) * len(g.entries) * g.kv_heads * g.head_dim * g.k.element_size()
+        return sum(len(g.entries) * g.kv_heads * (g.head_dim + g.value_dim) * g.k.element_size()
                    for g in self.groups)
 
     # -- telemetry (crates/nnis-rt/src/kv_telemetry.rs:42-80) ----------------
@@ -292,7 +300,8 @@ class CacheManager:
             "pages_held": [g.pool.held for g in self.groups], "pages_total": self.pages_total,
             "live_tokens": sum(self.lengths[s] for s in range(self.slots.count)
                                if self.slots.is_held(s)),
-            "kv_bytes": sum(g.k.numel() * g.k.element_size() * (2 if g.values else 1) for g in self.groups),
+            "kv_bytes": sum(t.numel() * t.element_size() for g in self.groups for t in (g.k, g.v)
+                            if t is not None),
         }
 
     def check(self) -> None:

@@ -16,6 +16,7 @@ from typing import Any, Dict, Mapping, Type
 
 from .llama import ConfigError, LlamaConfig
 from .nafezen import NafezenConfig
+from .tazadra import TazadraConfig
 from .spec import ModelSpec
 
 _ARCHITECTURES: Dict[str, Type] = {}
@@ -81,3 +82,4 @@ def spec_from_dir(model_dir: str) -> ModelSpec:
 
 register_architecture(LlamaConfig.architecture, LlamaConfig)
 register_architecture(NafezenConfig.architecture, NafezenConfig)
+register_architecture(TazadraConfig.architecture, TazadraConfig)

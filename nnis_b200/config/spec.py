@@ -43,6 +43,8 @@ class LayerSpec:
     prefix: str
     block: str
     parts: Mapping[str, PartSpec]
+    # constants of the arrangement itself (a multiplier of its branches, say)
+    params: Mapping[str, Any] = field(default_factory=dict)
 
     def part(self, role: str) -> PartSpec:
         if role not in self.parts:

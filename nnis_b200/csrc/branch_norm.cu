@@ -1,0 +1,156 @@
+// Row-wise kernels of the arrangement whose norm stands on a sub-layer's OUTPUT:
+//
+//   cast_rows        x = the float32 residual rows in the operand dtype: what the
+//                    sub-layers of such a block read (they read the stream itself)
+//   norm_scale_add   hidden += mult * rmsnorm(branch) * w, where `branch` is what a
+//                    sub-layer added up in float32; optionally also the new rows in the
+//                    operand dtype, for the sub-layer that reads them next
+//   glu_clamp        the feed-forward activation g' sigmoid(alpha g') (u' + 1) with
+//                    g' = min(g, limit), u' = clamp(u, -limit, limit)
+//   tanh_rows        tanh of float32 rows, rounded once to the operand dtype
+//   softcap_rows     x <- cap * tanh(x / cap), float32 in place (logits)
+//
+// Norm statistics, the scale and the sum are float32 in every dtype.
+#include "async_copy.cuh"
+#include "common.cuh"
+
+namespace nnis {
+
+template <typename T>
+__global__ void cast_rows_kernel(const float* __restrict__ x, T* __restrict__ out, size_t count) {
+    pdl_wait();
+    pdl_launch_dependents();
+    size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
+    if (i + 4 <= count) {
+        store4(out + i, load4(x + i));
+    } else {
+        for (; i < count; ++i) out[i] = from_float<T>(x[i]);
+    }
+}
+
+// a CTA of 256 threads per row
+template <typename T>
+__global__ void __launch_bounds__(256)
+norm_scale_add_kernel(const float* __restrict__ branch, const float* __restrict__ w,
+                      float* __restrict__ hidden, T* __restrict__ out, int width, float eps, float mult) {
+    __shared__ float red[8];
+    pdl_wait();
+    pdl_launch_dependents();
+    const size_t row = blockIdx.x;
+    const float* b = branch + row * width;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < width; i += 256) ss = fmaf(b[i], b[i], ss);
+    ss = warp_sum(ss);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    float total = 0.f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) total += red[k];
+    const float s = mult / sqrtf(total / (float)width + eps);
+    float* h = hidden + row * width;
+    for (int i = threadIdx.x; i < width; i += 256) {
+        float v = fmaf(b[i] * s, w[i], h[i]);
+        h[i] = v;
+        if (out) out[row * width + i] = from_float<T>(v);
+    }
+}
+
+template <typename T>
+__global__ void glu_clamp_kernel(const float* __restrict__ gate_up, T* __restrict__ out, size_t n_rows,
+                                 int inter, float limit, float alpha) {
+    pdl_wait();
+    pdl_launch_dependents();
+    size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= n_rows * (size_t)inter) return;
+    size_t r = idx / inter;
+    int i = (int)(idx - r * inter);
+    float g = fminf(gate_up[r * 2 * inter + i], limit);
+    float u = fminf(fmaxf(gate_up[r * 2 * inter + inter + i], -limit), limit);
+    float y = g / (1.0f + expf(-alpha * g)) * (u + 1.0f);
+    out[idx] = from_float<T>(y);
+}
+
+template <typename T>
+__global__ void tanh_rows_kernel(const float* __restrict__ x, T* __restrict__ out, size_t count) {
+    pdl_wait();
+    pdl_launch_dependents();
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < count) out[i] = from_float<T>(tanhf(x[i]));
+}
+
+__global__ void softcap_rows_kernel(float* __restrict__ x, size_t count, float cap) {
+    pdl_wait();
+    pdl_launch_dependents();
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < count) x[i] = cap * tanhf(x[i] / cap);
+}
+
+}  // namespace nnis
+
+using namespace nnis;
+
+NNIS_API int nnis_cast_rows(const float* x, void* out, int out_dtype, long long count, cudaStream_t stream) {
+    if (count <= 0 || !x || !out) return NNIS_ERR_ARGUMENT;
+    unsigned blocks = (unsigned)(((count + 3) / 4 + 255) / 256);
+    cudaError_t e;
+    if (out_dtype == NNIS_DTYPE_F32)
+        e = launch_dependent(cast_rows_kernel<float>, blocks, 256, 0, stream, x, (float*)out, (size_t)count);
+    else if (out_dtype == NNIS_DTYPE_BF16)
+        e = launch_dependent(cast_rows_kernel<bf16>, blocks, 256, 0, stream, x, (bf16*)out, (size_t)count);
+    else
+        return NNIS_ERR_UNSUPPORTED;
+    return e == cudaSuccess ? NNIS_OK : (int)e;
+}
+
+// out may be null (no copy in the operand dtype is wanted)
+NNIS_API int nnis_norm_scale_add(const float* branch, const float* w, float* hidden, void* out, int out_dtype,
+                                 int n_rows, int width, float eps, float mult, cudaStream_t stream) {
+    if (n_rows <= 0 || width <= 0 || !(eps > 0.f) || !branch || !w || !hidden) return NNIS_ERR_ARGUMENT;
+    cudaError_t e;
+    if (out_dtype == NNIS_DTYPE_F32)
+        e = launch_dependent(norm_scale_add_kernel<float>, (unsigned)n_rows, 256, 0, stream, branch, w, hidden,
+                             (float*)out, width, eps, mult);
+    else if (out_dtype == NNIS_DTYPE_BF16)
+        e = launch_dependent(norm_scale_add_kernel<bf16>, (unsigned)n_rows, 256, 0, stream, branch, w, hidden,
+                             (bf16*)out, width, eps, mult);
+    else
+        return NNIS_ERR_UNSUPPORTED;
+    return e == cudaSuccess ? NNIS_OK : (int)e;
+}
+
+NNIS_API int nnis_glu_clamp(const float* gate_up, void* out, int out_dtype, long long n_rows, int inter,
+                            float limit, float alpha, cudaStream_t stream) {
+    if (n_rows <= 0 || inter <= 0 || !(limit > 0.f)) return NNIS_ERR_ARGUMENT;
+    size_t total = (size_t)n_rows * inter;
+    unsigned blocks = (unsigned)((total + 255) / 256);
+    cudaError_t e;
+    if (out_dtype == NNIS_DTYPE_F32)
+        e = launch_dependent(glu_clamp_kernel<float>, blocks, 256, 0, stream, gate_up, (float*)out, (size_t)n_rows,
+                             inter, limit, alpha);
+    else if (out_dtype == NNIS_DTYPE_BF16)
+        e = launch_dependent(glu_clamp_kernel<bf16>, blocks, 256, 0, stream, gate_up, (bf16*)out, (size_t)n_rows,
+                             inter, limit, alpha);
+    else
+        return NNIS_ERR_UNSUPPORTED;
+    return e == cudaSuccess ? NNIS_OK : (int)e;
+}
+
+NNIS_API int nnis_tanh_rows(const float* x, void* out, int out_dtype, long long count, cudaStream_t stream) {
+    if (count <= 0 || !x || !out) return NNIS_ERR_ARGUMENT;
+    unsigned blocks = (unsigned)((count + 255) / 256);
+    cudaError_t e;
+    if (out_dtype == NNIS_DTYPE_F32)
+        e = launch_dependent(tanh_rows_kernel<float>, blocks, 256, 0, stream, x, (float*)out, (size_t)count);
+    else if (out_dtype == NNIS_DTYPE_BF16)
+        e = launch_dependent(tanh_rows_kernel<bf16>, blocks, 256, 0, stream, x, (bf16*)out, (size_t)count);
+    else
+        return NNIS_ERR_UNSUPPORTED;
+    return e == cudaSuccess ? NNIS_OK : (int)e;
+}
+
+NNIS_API int nnis_softcap_rows(float* x, long long count, float cap, cudaStream_t stream) {
+    if (count <= 0 || !x || !(cap > 0.f)) return NNIS_ERR_ARGUMENT;
+    unsigned blocks = (unsigned)((count + 255) / 256);
+    cudaError_t e = launch_dependent(softcap_rows_kernel, blocks, 256, 0, stream, x, (size_t)count, cap);
+    return e == cudaSuccess ? NNIS_OK : (int)e;
+}

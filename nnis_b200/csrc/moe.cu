@@ -8,7 +8,17 @@
 //   moe_down    residual[n, :] += sum_s weight[n, s] W_down[id[n, s]] act[n, s, :], the
 //               chosen experts added in the router's order (the same bits every time)
 //
-// Expert weights are stacked: W_up [experts, ff, width], W_down [experts, width, ff].
+// A second form serves routers whose scores are sigmoid(z), used as they are (not
+// renormalised) and applied to the expert's INPUT, with gated experts
+// W_down (silu(W_gate x) * (W_up x)), x = score * h:
+//
+//   moe_route      with `sigmoid_scores`: the same choice, weights = sigmoid of the chosen logits
+//   moe_up_gated   act[n, s, :] = silu(w g) * (w u) with g = W_gate h, u = W_up h and w the score:
+//                  the score multiplies both float32 sums, which is the product with w * h
+//   moe_down       with no weights: the chosen experts' outputs are added as they are
+//
+// Expert weights are stacked: W_up [experts, ff, width] (gated: [experts, 2 ff, width], gate rows
+// first), W_down [experts, width, ff].
 // A row whose position is -1 (padding) is skipped everywhere.
 #include <float.h>
 
@@ -44,7 +54,8 @@ template <typename T>
 __global__ void __launch_bounds__(256)
 moe_route_kernel(const T* __restrict__ h, const float* __restrict__ wr, const float* __restrict__ br,
                  const int* __restrict__ token_pos, int* __restrict__ ids,
-                 float* __restrict__ weights, int n_tokens, int width, int experts, int top) {
+                 float* __restrict__ weights, int n_tokens, int width, int experts, int top,
+                 int sigmoid_scores) {
     extern __shared__ float z[];  // [experts]
     pdl_wait();
     pdl_launch_dependents();
@@ -91,7 +102,7 @@ moe_route_kernel(const T* __restrict__ h, const float* __restrict__ wr, const fl
             }
         }
         if (s == 0) first = best;
-        float p = expf(best - first);
+        float p = sigmoid_scores ? 1.0f / (1.0f + expf(-best)) : expf(best - first);
         total += p;
         if (lane == 0) {
             id[s] = arg;
@@ -100,6 +111,7 @@ moe_route_kernel(const T* __restrict__ h, const float* __restrict__ wr, const fl
         }
         __syncwarp();
     }
+    if (sigmoid_scores) return;  // (used as they are)
     float inv = 1.0f / total;
     __syncwarp();
     for (int s = lane; s < top; s += 32) wt[s] *= inv;
@@ -127,6 +139,31 @@ moe_up_kernel(const T* __restrict__ h, const T* __restrict__ w_up, const int* __
 
 template <typename T>
 __global__ void __launch_bounds__(256)
+moe_up_gated_kernel(const T* __restrict__ h, const T* __restrict__ w_gu, const int* __restrict__ ids,
+                    const float* __restrict__ weights, const int* __restrict__ token_pos, T* __restrict__ act,
+                    int width, int ff, int top) {
+    pdl_wait();
+    pdl_launch_dependents();
+    int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    long long pair = blockIdx.x;
+    int f = blockIdx.y * 8 + warp;
+    long long n = pair / top;
+    if (f >= ff || token_pos[n] < 0) return;
+    const T* wg = w_gu + ((size_t)ids[pair] * 2 * ff + f) * width;
+    const T* wu = wg + (size_t)ff * width;
+    const T* x = h + (size_t)n * width;
+    float g = warp_row_dot(wg, x, width, lane);
+    float u = warp_row_dot(wu, x, width, lane);
+    if (lane == 0) {
+        float w = weights ? weights[pair] : 1.0f;
+        g *= w;
+        u *= w;
+        act[(size_t)pair * ff + f] = from_float<T>(g / (1.0f + expf(-g)) * u);
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
 moe_down_kernel(const T* __restrict__ act, const T* __restrict__ w_down, const int* __restrict__ ids,
                 const float* __restrict__ weights, const int* __restrict__ token_pos,
                 float* __restrict__ residual, int width, int ff, int top) {
@@ -141,7 +178,7 @@ moe_down_kernel(const T* __restrict__ act, const T* __restrict__ w_down, const i
         const T* w = w_down + ((size_t)ids[n * top + s] * width + c) * ff;
         const T* a = act + ((size_t)n * top + s) * ff;
         float acc = warp_row_dot(w, a, ff, lane);
-        sum = fmaf(weights[n * top + s], acc, sum);
+        sum = weights ? fmaf(weights[n * top + s], acc, sum) : sum + acc;
     }
     if (lane == 0) residual[(size_t)n * width + c] += sum;
 }
@@ -152,7 +189,7 @@ using namespace nnis;
 
 NNIS_API int nnis_moe_route(const void* h, const float* wr, const float* br, const int* token_pos,
                             int* ids, float* weights, int n_tokens, int width, int experts, int top,
-                            int dtype, cudaStream_t stream) {
+                            int sigmoid_scores, int dtype, cudaStream_t stream) {
     if (n_tokens <= 0 || width <= 0 || experts <= 0 || top <= 0 || top > experts || !h || !wr || !ids ||
         !weights || !token_pos)
         return NNIS_ERR_ARGUMENT;
@@ -162,10 +199,10 @@ NNIS_API int nnis_moe_route(const void* h, const float* wr, const float* br, con
     cudaError_t e;
     if (dtype == NNIS_DTYPE_F32)
         e = launch_dependent(moe_route_kernel<float>, blocks, 256, smem, stream, (const float*)h, wr, br, token_pos,
-                             ids, weights, n_tokens, width, experts, top);
+                             ids, weights, n_tokens, width, experts, top, sigmoid_scores);
     else if (dtype == NNIS_DTYPE_BF16)
         e = launch_dependent(moe_route_kernel<bf16>, blocks, 256, smem, stream, (const bf16*)h, wr, br, token_pos,
-                             ids, weights, n_tokens, width, experts, top);
+                             ids, weights, n_tokens, width, experts, top, sigmoid_scores);
     else
         return NNIS_ERR_UNSUPPORTED;
     return e == cudaSuccess ? NNIS_OK : (int)e;
@@ -195,6 +232,37 @@ NNIS_API int nnis_moe_experts(const void* h, const void* w_up, const void* w_dow
         if (e == cudaSuccess)
             e = launch_dependent(moe_down_kernel<bf16>, down_grid, 256, 0, stream, (const bf16*)act,
                                  (const bf16*)w_down, ids, weights, token_pos, residual, width, ff, top);
+    } else {
+        return NNIS_ERR_UNSUPPORTED;
+    }
+    return e == cudaSuccess ? NNIS_OK : (int)e;
+}
+
+// The gated form: w_gu [experts, 2 ff, width]; the weights multiply the experts' inputs.
+NNIS_API int nnis_moe_experts_gated(const void* h, const void* w_gu, const void* w_down, const int* ids,
+                                    const float* weights, const int* token_pos, void* act, float* residual,
+                                    int n_tokens, int width, int ff, int top, int dtype, cudaStream_t stream) {
+    if (n_tokens <= 0 || width <= 0 || ff <= 0 || top <= 0 || !h || !w_gu || !w_down || !ids || !weights ||
+        !token_pos || !act || !residual)
+        return NNIS_ERR_ARGUMENT;
+    if ((ff + 7) / 8 > 65535 || (width + 7) / 8 > 65535) return NNIS_ERR_UNSUPPORTED;
+    dim3 up_grid((unsigned)((long long)n_tokens * top), (ff + 7) / 8);
+    dim3 down_grid(n_tokens, (width + 7) / 8);
+    cudaError_t e;
+    if (dtype == NNIS_DTYPE_F32) {
+        e = launch_dependent(moe_up_gated_kernel<float>, up_grid, 256, 0, stream, (const float*)h, (const float*)w_gu,
+                             ids, weights, token_pos, (float*)act, width, ff, top);
+        if (e == cudaSuccess)
+            e = launch_dependent(moe_down_kernel<float>, down_grid, 256, 0, stream, (const float*)act,
+                                 (const float*)w_down, ids, (const float*)nullptr, token_pos, residual, width, ff,
+                                 top);
+    } else if (dtype == NNIS_DTYPE_BF16) {
+        e = launch_dependent(moe_up_gated_kernel<bf16>, up_grid, 256, 0, stream, (const bf16*)h, (const bf16*)w_gu,
+                             ids, weights, token_pos, (bf16*)act, width, ff, top);
+        if (e == cudaSuccess)
+            e = launch_dependent(moe_down_kernel<bf16>, down_grid, 256, 0, stream, (const bf16*)act,
+                                 (const bf16*)w_down, ids, (const float*)nullptr, token_pos, residual, width, ff,
+                                 top);
     } else {
         return NNIS_ERR_UNSUPPORTED;
     }

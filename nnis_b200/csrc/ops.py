@@ -1116,9 +1116,11 @@ def retention_segments(counts, seg_len: int):
 
 
 def moe_route(h: torch.Tensor, w_router: torch.Tensor, b_router: Optional[torch.Tensor],
-              token_pos: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, top: int) -> None:
+              token_pos: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, top: int,
+              sigmoid_scores: bool = False) -> None:
     """ids, weights [n, top]: the ``top`` experts with the largest float32 logits
-    w_router . h + b_router and the softmax over their logits."""
+    w_router . h + b_router and the softmax over their logits; with ``sigmoid_scores`` the
+    weights are the sigmoid of each chosen logit, not renormalised."""
     _cuda(h, w_router, b_router, token_pos, ids, weights)
     n, width = h.shape
     experts = w_router.shape[0]
@@ -1128,7 +1130,8 @@ def moe_route(h: torch.Tensor, w_router: torch.Tensor, b_router: Optional[torch.
     _need(ids.dtype == torch.int32 and weights.dtype == torch.float32 and ids.numel() >= n * top
           and weights.numel() >= n * top and 0 < top <= experts, "moe_route: ids int32, weights float32 [n, top]")
     _check(_lib().nnis_moe_route(_ptr(h), _ptr(w_router), _ptr(b_router), _ptr(token_pos), _ptr(ids),
-                                 _ptr(weights), n, width, experts, top, code_of(h.dtype), _stream()),
+                                 _ptr(weights), n, width, experts, top, 1 if sigmoid_scores else 0,
+                                 code_of(h.dtype), _stream()),
            "moe_route")
 
 
@@ -1261,3 +1264,236 @@ def moe_grouped_tc(h: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor, id
                                       _ptr(place), _ptr(tile_expert), _ptr(x_sorted), _ptr(act), _ptr(y),
                                       _ptr(residual), n, width, ff, experts, top, sm_count(h.device),
                                       _ptr(status_word(h.device)), PDL, _stream()), "moe_grouped_tc", 5)
+
+
+# ---------------------------------------------------------------------------
+# a norm on a sub-layer's output, activations, WKV, selective scan, attention with a sink
+def cast_rows(x: torch.Tensor, out: torch.Tensor) -> None:
+    """out = x (float32) in out's dtype, rounded once."""
+    _cuda(x, out)
+    _need(x.dtype == torch.float32 and x.numel() == out.numel(), "cast_rows: float32 in, as many values out")
+    _check(_lib().nnis_cast_rows(_ptr(x), _ptr(out), code_of(out.dtype), ctypes.c_longlong(x.numel()),
+                                 _stream()), "cast_rows")
+
+
+def norm_scale_add(branch: torch.Tensor, weight: torch.Tensor, eps: float, mult: float,
+                   hidden: torch.Tensor, out: Optional[torch.Tensor] = None) -> None:
+    """hidden += mult * rmsnorm(branch) * weight (all float32); ``out``, if given, receives the
+    new rows of hidden in its own dtype."""
+    _cuda(branch, weight, hidden, out)
+    n, width = hidden.shape
+    _need(branch.dtype == hidden.dtype == weight.dtype == torch.float32 and tuple(branch.shape) == (n, width)
+          and weight.numel() == width, "norm_scale_add: float32 [n, width] rows and [width] weights")
+    _need(out is None or tuple(out.shape) == (n, width), "norm_scale_add: out [n, width]")
+    _check(_lib().nnis_norm_scale_add(_ptr(branch), _ptr(weight), _ptr(hidden), _ptr(out),
+                                      code_of(out.dtype) if out is not None else F32, n, width,
+                                      ctypes.c_float(eps), ctypes.c_float(mult), _stream()), "norm_scale_add")
+
+
+def glu_clamp(gate_up: torch.Tensor, out: torch.Tensor, limit: float, alpha: float) -> None:
+    """out = g' * sigmoid(alpha * g') * (u' + 1) with g' = min(gate, limit) and u' = up clamped
+    to [-limit, limit]; gate_up float32 [n, 2I] (gate columns first)."""
+    _cuda(gate_up, out)
+    n, inter = out.shape
+    _need(gate_up.dtype == torch.float32 and tuple(gate_up.shape) == (n, 2 * inter),
+          "glu_clamp: gate_up float32 [n, 2 * inter]")
+    _check(_lib().nnis_glu_clamp(_ptr(gate_up), _ptr(out), code_of(out.dtype), ctypes.c_longlong(n), inter,
+                                 ctypes.c_float(limit), ctypes.c_float(alpha), _stream()), "glu_clamp")
+
+
+def tanh_rows(x: torch.Tensor, out: torch.Tensor) -> None:
+    _cuda(x, out)
+    _need(x.dtype == torch.float32 and x.numel() == out.numel(), "tanh_rows: float32 in, as many values out")
+    _check(_lib().nnis_tanh_rows(_ptr(x), _ptr(out), code_of(out.dtype), ctypes.c_longlong(x.numel()),
+                                 _stream()), "tanh_rows")
+
+
+def softcap_rows(x: torch.Tensor, cap: float) -> None:
+    """x <- cap * tanh(x / cap), float32 in place."""
+    _cuda(x)
+    _need(x.dtype == torch.float32 and cap > 0, "softcap_rows: float32 rows, a positive cap")
+    if x.numel():
+        _check(_lib().nnis_softcap_rows(_ptr(x), ctypes.c_longlong(x.numel()), ctypes.c_float(cap), _stream()),
+               "softcap_rows")
+
+
+def _seq_tables(token_pos, token_seq, seq_slots, seq_first_row, seq_count):
+    _cuda(token_pos, token_seq, seq_slots, seq_first_row, seq_count)
+    for t in (token_pos, token_seq, seq_slots, seq_first_row, seq_count):
+        _need(t is None or t.dtype == torch.int32, "step tables: int32")
+    _need((seq_first_row is None) == (seq_count is None), "seq_first_row and seq_count come together")
+
+
+def wkv_mix(x: torch.Tensor, mu: torch.Tensor, prev: torch.Tensor, token_pos: torch.Tensor,
+            token_seq: torch.Tensor, seq_slots: torch.Tensor, seq_first_row: Optional[torch.Tensor],
+            seq_count: Optional[torch.Tensor], mixes: torch.Tensor) -> None:
+    """mixes[s, n] = x[n] + (x'[n] - x[n]) * mu[s], x' the row of the token before (the row above,
+    or ``prev[slot]`` for a step's first token of a sequence)."""
+    _cuda(x, mu, prev, mixes)
+    _seq_tables(token_pos, token_seq, seq_slots, seq_first_row, seq_count)
+    n, width = x.shape
+    streams = mu.shape[0]
+    _need(mu.dtype == prev.dtype == torch.float32 and mu.shape[1] == width and prev.shape[1] == width,
+          "wkv_mix: mu [streams, width], prev [slots, width] float32")
+    _need(mixes.dtype == x.dtype and tuple(mixes.shape) == (streams, n, width), "wkv_mix: mixes [streams, n, width]")
+    _check(_lib().nnis_wkv_mix(_ptr(x), _ptr(mu), _ptr(prev), _ptr(token_pos), _ptr(token_seq), _ptr(seq_slots),
+                               _ptr(seq_first_row), _ptr(seq_count), _ptr(mixes), n, width, streams,
+                               code_of(x.dtype), _stream()), "wkv_mix")
+
+
+def wkv_scan(r: torch.Tensor, k: torch.Tensor, v: torch.Tensor, d: torch.Tensor, u: torch.Tensor,
+             state: torch.Tensor, token_pos: torch.Tensor, token_seq: torch.Tensor, seq_slots: torch.Tensor,
+             seq_first_row: Optional[torch.Tensor], seq_count: Optional[torch.Tensor], o_raw: torch.Tensor,
+             heads: int, dim: int) -> None:
+    """The recurrence over the step's tokens, from and into ``state`` [slots, heads, dim, dim]."""
+    _cuda(r, k, v, d, u, state, o_raw)
+    _seq_tables(token_pos, token_seq, seq_slots, seq_first_row, seq_count)
+    n = r.shape[0]
+    _need(r.dtype == k.dtype == v.dtype and tuple(r.shape) == tuple(k.shape) == tuple(v.shape) == (n, heads * dim),
+          "wkv_scan: r, k, v [n, heads * dim] of one dtype")
+    _need(d.dtype == u.dtype == state.dtype == o_raw.dtype == torch.float32 and d.numel() == n * heads * dim
+          and u.numel() == heads * dim and o_raw.numel() >= n * heads * dim
+          and tuple(state.shape[1:]) == (heads, dim, dim), "wkv_scan: float32 decay rows, bonus, state, output")
+    _need(dim <= 256, f"wkv_scan: heads of {dim} channels (at most 256)")
+    units = seq_first_row.numel() if seq_first_row is not None else n
+    _check(_lib().nnis_wkv_scan(_ptr(r), _ptr(k), _ptr(v), _ptr(d), _ptr(u), _ptr(state), _ptr(token_pos),
+                                _ptr(token_seq), _ptr(seq_slots), _ptr(seq_first_row), _ptr(seq_count),
+                                _ptr(o_raw), units, heads, dim, code_of(r.dtype), _stream()), "wkv_scan")
+
+
+def wkv_finish(o_raw: torch.Tensor, gate: torch.Tensor, norm_w: torch.Tensor, x: torch.Tensor,
+               prev: torch.Tensor, token_pos: torch.Tensor, token_seq: torch.Tensor, seq_slots: torch.Tensor,
+               seq_first_row: Optional[torch.Tensor], seq_count: Optional[torch.Tensor], out: torch.Tensor,
+               heads: int, dim: int, eps: float) -> None:
+    """out = o / rms(o) per head * norm_w * silu(gate); prev[slot] = the step's last row of x."""
+    _cuda(o_raw, gate, norm_w, x, prev, out)
+    _seq_tables(token_pos, token_seq, seq_slots, seq_first_row, seq_count)
+    n, width = x.shape
+    _need(gate.dtype == out.dtype == x.dtype and tuple(gate.shape) == tuple(out.shape) == (n, heads * dim),
+          "wkv_finish: gate, out [n, heads * dim]")
+    _need(o_raw.dtype == norm_w.dtype == prev.dtype == torch.float32 and norm_w.numel() == heads * dim
+          and prev.shape[1] == width, "wkv_finish: float32 o_raw, norm weights, prev [slots, width]")
+    _check(_lib().nnis_wkv_finish(_ptr(o_raw), _ptr(gate), _ptr(norm_w), _ptr(x), _ptr(prev), _ptr(token_pos),
+                                  _ptr(token_seq), _ptr(seq_slots), _ptr(seq_first_row), _ptr(seq_count),
+                                  _ptr(out), n, heads, dim, width, ctypes.c_float(eps), code_of(x.dtype),
+                                  _stream()), "wkv_finish")
+
+
+def conv_silu(xz: torch.Tensor, conv_w: torch.Tensor, conv_b: Optional[torch.Tensor], conv_state: torch.Tensor,
+              token_pos: torch.Tensor, token_seq: torch.Tensor, seq_slots: torch.Tensor,
+              seq_first_row: Optional[torch.Tensor], xc: torch.Tensor) -> None:
+    """xc = silu(causal convolution per channel of the first ``inner`` columns of xz [n, 2 inner]);
+    conv_w [inner, taps] (last column: the current token), conv_state [slots, taps - 1, inner]."""
+    _cuda(xz, conv_w, conv_b, conv_state, xc, token_pos, token_seq, seq_slots, seq_first_row)
+    n, inner = xc.shape
+    taps = conv_w.shape[1]
+    _need(xz.dtype == xc.dtype and tuple(xz.shape) == (n, 2 * inner), "conv_silu: xz [n, 2 * inner]")
+    _need(conv_w.dtype == conv_state.dtype == torch.float32 and conv_w.shape[0] == inner
+          and conv_state.dim() == 3 and conv_state.shape[1] >= taps - 1 and conv_state.shape[2] == inner,
+          "conv_silu: float32 conv_w [inner, taps], conv_state [slots, taps - 1, inner]")
+    _need(conv_state.shape[1] == max(taps - 1, 1), "conv_silu: conv_state holds taps - 1 rows a slot (one at least)")
+    _check(_lib().nnis_conv_silu(_ptr(xz), _ptr(conv_w), _ptr(conv_b), _ptr(conv_state), _ptr(token_pos),
+                                 _ptr(token_seq), _ptr(seq_slots), _ptr(seq_first_row), _ptr(xc), n, inner, taps,
+                                 code_of(xc.dtype), _stream()), "conv_silu")
+
+
+def selective_scan(xc: torch.Tensor, xz: torch.Tensor, dt_raw: torch.Tensor, bc: torch.Tensor,
+                   a_log: torch.Tensor, dskip: torch.Tensor, state: torch.Tensor, conv_state: torch.Tensor,
+                   token_pos: torch.Tensor, token_seq: torch.Tensor, seq_slots: torch.Tensor,
+                   seq_first_row: Optional[torch.Tensor], seq_count: Optional[torch.Tensor], y: torch.Tensor,
+                   taps: int) -> None:
+    """y = (scan over the step's tokens + D * xc) * silu(z), from and into ``state`` [slots, inner, N];
+    moves ``conv_state`` on by the step's inputs."""
+    _cuda(xc, xz, dt_raw, bc, a_log, dskip, state, conv_state, y)
+    _seq_tables(token_pos, token_seq, seq_slots, seq_first_row, seq_count)
+    n, inner = xc.shape
+    N = a_log.shape[1]
+    _need(xz.dtype == xc.dtype == y.dtype and tuple(xz.shape) == (n, 2 * inner) and tuple(y.shape) == (n, inner),
+          "selective_scan: xc, y [n, inner], xz [n, 2 * inner]")
+    _need(dt_raw.dtype == bc.dtype == a_log.dtype == dskip.dtype == state.dtype == torch.float32
+          and tuple(dt_raw.shape) == (n, inner) and tuple(bc.shape) == (n, 2 * N) and a_log.shape[0] == inner
+          and dskip.numel() == inner and tuple(state.shape[1:]) == (inner, N),
+          "selective_scan: float32 dt [n, inner], bc [n, 2 N], A_log [inner, N], D [inner], state")
+    _need(N <= 384, f"selective_scan: {N} state values a channel (at most 384)")
+    units = seq_first_row.numel() if seq_first_row is not None else n
+    _check(_lib().nnis_selective_scan(_ptr(xc), _ptr(xz), _ptr(dt_raw), _ptr(bc), _ptr(a_log), _ptr(dskip),
+                                      _ptr(state), _ptr(conv_state), _ptr(token_pos), _ptr(token_seq),
+                                      _ptr(seq_slots), _ptr(seq_first_row), _ptr(seq_count), _ptr(y), units, inner,
+                                      N, taps, code_of(xc.dtype), _stream()), "selective_scan")
+
+
+def qkv_prep(a: torch.Tensor, wq: Optional[torch.Tensor], wk: Optional[torch.Tensor],
+             freq: Optional[torch.Tensor], token_pos: torch.Tensor, token_seq: torch.Tensor,
+             page_table: Optional[torch.Tensor], q_out: torch.Tensor, k_cache: Optional[torch.Tensor],
+             v_cache: Optional[torch.Tensor], gate_out: Optional[torch.Tensor], heads: int, kv_heads: int,
+             dk: int, dv: int, rot: int, eps: float) -> None:
+    """From float32 rows [q | k | v | gate logits]: norms of q and k over their whole projections,
+    rotation of neighbouring pairs, q packed, k and v into the cache, sigmoid of the gate.
+    ``kv_heads == 0``: the rows hold no keys and values."""
+    _cuda(a, wq, wk, freq, token_pos, token_seq, page_table, q_out, k_cache, v_cache, gate_out)
+    n = a.shape[0]
+    gated = gate_out is not None
+    _need(a.dtype == torch.float32 and a.shape[1] == heads * dk + kv_heads * (dk + dv) + (heads if gated else 0),
+          "qkv_prep: float32 rows [q | k | v | gate]")
+    _need(tuple(q_out.shape) == (n, heads * dk), "qkv_prep: q_out [n, heads * dk]")
+    for w, size in ((wq, heads * dk), (wk, kv_heads * dk)):
+        _need(w is None or (w.dtype == torch.float32 and w.numel() == size), "qkv_prep: float32 norm weights")
+    _need(rot == 0 or (freq is not None and freq.dtype == torch.float32 and freq.numel() >= rot // 2),
+          "qkv_prep: freq float32 [rot / 2]")
+    cols, page_size = 0, 1
+    if kv_heads:
+        _need(k_cache.dtype == v_cache.dtype == q_out.dtype and tuple(k_cache.shape[1:3]) == tuple(v_cache.shape[1:3])
+              and k_cache.shape[1] == kv_heads and k_cache.shape[3] == dk and v_cache.shape[3] == dv,
+              "qkv_prep: caches [pages, kv_heads, page, dk] and [.., dv]")
+        _need(page_table is not None and page_table.dtype == torch.int32, "qkv_prep: page_table int32")
+        cols, page_size = page_table.shape[1], k_cache.shape[2]
+    _check(_lib().nnis_qkv_prep(_ptr(a), _ptr(wq), _ptr(wk), _ptr(freq), _ptr(token_pos), _ptr(token_seq),
+                                _ptr(page_table), cols, _ptr(q_out), _ptr(k_cache), _ptr(v_cache), _ptr(gate_out),
+                                n, heads, kv_heads, dk, dv, rot, 1 if gated else 0, page_size, ctypes.c_float(eps),
+                                code_of(q_out.dtype), _stream()), "qkv_prep")
+
+
+def attention_sink(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, token_pos: torch.Tensor,
+                   token_seq: torch.Tensor, page_table: torch.Tensor, sink: Optional[torch.Tensor],
+                   gate: Optional[torch.Tensor], out: torch.Tensor, heads: int, kv_heads: int, window: int,
+                   chunk: int, scale: float, cap: float, n_splits: int = 1,
+                   partial: Optional[torch.Tensor] = None) -> None:
+    """Causal attention of packed queries over the paged cache with a soft cap on the scores, a
+    chunked and/or windowed mask, a sink per head in the denominator and a gate per (token, head)."""
+    _cuda(q, k_cache, v_cache, token_pos, token_seq, page_table, sink, gate, out, partial)
+    n = out.shape[0]
+    pages, nkv, page_size, dk = k_cache.shape
+    dv = v_cache.shape[3]
+    _need(nkv == kv_heads and tuple(v_cache.shape[:3]) == (pages, nkv, page_size) and heads % kv_heads == 0,
+          "attention_sink: caches [pages, kv_heads, page, dk / dv]")
+    _need(q.dtype == k_cache.dtype == v_cache.dtype == out.dtype and tuple(q.shape) == (n, heads * dk)
+          and tuple(out.shape) == (n, heads * dv), "attention_sink: q [n, heads * dk], out [n, heads * dv]")
+    _need(pages * nkv * page_size < 2 ** 31, "attention_sink: the cache has too many rows")
+    _need(sink is None or (sink.dtype == torch.float32 and sink.numel() == heads), "attention_sink: sink [heads]")
+    _need(gate is None or (gate.dtype == torch.float32 and gate.numel() >= n * heads), "attention_sink: gate")
+    if n_splits > 1:
+        _need(partial is not None and partial.dtype == torch.float32
+              and partial.numel() >= n * heads * n_splits * (dv + 2), "attention_sink: partial scratch")
+    _check(_lib().nnis_attention_sink(_ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(token_pos), _ptr(token_seq),
+                                      _ptr(page_table), page_table.shape[1], _ptr(sink), _ptr(gate), _ptr(out),
+                                      _ptr(partial), n, heads, kv_heads, dk, dv, page_size, window, chunk,
+                                      ctypes.c_float(scale), ctypes.c_float(cap), n_splits, code_of(out.dtype),
+                                      _stream()), "attention_sink", 2 if n_splits > 1 else 1)
+
+
+def moe_experts_gated(h: torch.Tensor, w_gu: torch.Tensor, w_down: torch.Tensor, ids: torch.Tensor,
+                      weights: torch.Tensor, token_pos: torch.Tensor, act: torch.Tensor,
+                      residual: torch.Tensor, top: int) -> None:
+    """residual[n] += sum over the chosen experts of W_down[e] (silu(W_gate[e] x) * (W_up[e] x)),
+    x = weight * h[n]; w_gu [experts, 2 ff, width] with the gate's rows first."""
+    _cuda(h, w_gu, w_down, ids, weights, token_pos, act, residual)
+    n, width = h.shape
+    experts, ff2, _ = w_gu.shape
+    ff = ff2 // 2
+    _need(tuple(w_gu.shape) == (experts, 2 * ff, width) and tuple(w_down.shape) == (experts, width, ff)
+          and h.dtype == w_gu.dtype == w_down.dtype == act.dtype, "moe_experts_gated: stacked weights of one dtype")
+    _need(act.numel() >= n * top * ff, "moe_experts_gated: act scratch [n, top, ff]")
+    _need(residual.dtype == torch.float32 and tuple(residual.shape) == (n, width), "moe_experts_gated: residual")
+    _check(_lib().nnis_moe_experts_gated(_ptr(h), _ptr(w_gu), _ptr(w_down), _ptr(ids), _ptr(weights),
+                                         _ptr(token_pos), _ptr(act), _ptr(residual), n, width, ff, top,
+                                         code_of(h.dtype), _stream()), "moe_experts_gated", 2)

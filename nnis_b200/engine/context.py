@@ -65,6 +65,11 @@ class StepContext:
     next_norm: object = None
     emit_for: object = None
     shared_norm: object = None
+    # The residual rows in the operand dtype, left by the kernel that wrote them last, for a
+    # block whose sub-layers read the stream itself (``parts.block.BranchNormBlock``); taken
+    # (and cleared) by the block that runs next.
+    hidden_copy: object = None
+    copy_turn: int = 0  # which of that block's two buffers was written last
 
     def take_shared_norm(self, norm):
         """What the part before left of ``norm``'s work, or None; nothing is kept."""

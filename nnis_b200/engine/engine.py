@@ -25,6 +25,7 @@ from ..config import read_config
 from ..csrc import ops
 from ..config.spec import ModelSpec
 from ..weights import load_weights
+from ..weights.loader import shape_fits
 from .context import StepContext
 from .model import DecoderModel
 from .workspace import Workspace
@@ -104,7 +105,7 @@ class Engine:
         kept = {}
         for name, ws in wanted.items():
             t = tensors[name]
-            if tuple(t.shape) != tuple(ws.shape):
+            if not shape_fits(tuple(t.shape), tuple(ws.shape)):
                 raise ValueError(f"{name}: shape {list(t.shape)}, expected {list(ws.shape)}")
             kept[name] = t.to(torch.float32 if ws.role == "vector" else compute).to(device).contiguous()
         return cls(spec, kept, dtype, device, **kwargs)

@@ -8,6 +8,10 @@ class registered in ``BLOCKS``, not a change here.
 
 ``parallel``: with n = norm(h), h += mixer(n) + ffn(n); roles norm, mixer, ffn.
 
+``branch_norm``: h += m * norm1(mixer(h)); h += m * norm2(ffn(h)): the sub-layers read the
+stream itself and the norm stands on their OUTPUT; roles mixer, mixer_norm, and optionally
+ffn, ffn_norm; ``LayerSpec.params["residual_mult"]`` is m.
+
 ``prenorm``: h += mixer(norm1(h)); h += ffn(norm2(h)) - the order of NNIS's
 decoder (crates/nnis-model/src/runtime.rs:946-1097); roles mixer_norm, mixer,
 ffn_norm, ffn.  In decode steps a norm may be shared out between the projections on
@@ -181,5 +185,61 @@ class ParallelBlock(Block):
             self.ffn.forward(normed, ctx, hidden)
 
 
+class BranchNormBlock(Block):
+    """A norm on each sub-layer's output and a multiplier: with m = ``residual_mult``,
+    x += m * norm1(mixer(x)), then x += m * norm2(ffn(x)).  The sub-layers read x itself (in
+    the operand dtype); each adds its output up in a zeroed float32 branch buffer, as it would
+    into the residual stream, and one kernel norms that buffer, scales it and adds it to the
+    stream.  In bfloat16 the same kernel leaves the new rows of the stream in bfloat16 for the
+    sub-layer that reads them next (``ctx.hidden_copy`` across blocks).  Roles: mixer,
+    mixer_norm and, optionally, ffn with ffn_norm.  The norms are RMS norms (``rmsnorm``)."""
+
+    def __init__(self, layer_spec, dtype: torch.dtype, device: torch.device):
+        super().__init__(layer_spec, dtype, device)
+        self.mult = float(layer_spec.params.get("residual_mult", 1.0))
+        self.mixer = self.build(MIXERS, "mixer")
+        self.mixer_norm = self.build(NORMS, "mixer_norm")
+        self.ffn = self.build(FEED_FORWARDS, "ffn") if "ffn" in layer_spec.parts else None
+        self.ffn_norm = self.build(NORMS, "ffn_norm") if self.ffn is not None else None
+        for norm in (self.mixer_norm, self.ffn_norm):
+            if norm is not None and getattr(norm, "kind", None) != "rmsnorm":
+                raise ValueError("branch_norm: the norm on a sub-layer's output is an rmsnorm")
+
+    def parts(self):
+        return tuple(p for p in (self.mixer, self.mixer_norm, self.ffn, self.ffn_norm) if p is not None)
+
+    def _close(self, branch, norm, hidden, ctx, n, width):
+        """hidden += m * norm(branch); returns what the next sub-layer reads."""
+        if self.dtype == torch.float32:
+            ops.norm_scale_add(branch, norm.weight, norm.eps, self.mult, hidden)
+            return hidden
+        # (two buffers in turn: the sub-layer that just ran may still be the reader of one)
+        ctx.copy_turn = 1 - getattr(ctx, "copy_turn", 0)
+        x = ctx.workspace.get(f"stream_copy{ctx.copy_turn}", (n, width), self.dtype)
+        ops.norm_scale_add(branch, norm.weight, norm.eps, self.mult, hidden, x)
+        return x
+
+    def forward(self, hidden: torch.Tensor, ctx, cache) -> None:
+        n, width = hidden.shape
+        ws = ctx.workspace
+        ctx.emit_for = None  # no part may begin a norm here: none reads the stream
+        x, ctx.hidden_copy = ctx.hidden_copy, None
+        if self.dtype == torch.float32:
+            x = hidden
+        elif x is None:
+            x = ws.get("stream_copy_first", (n, width), self.dtype)
+            ops.cast_rows(hidden, x)
+        branch = ws.get("branch_out", (n, width), torch.float32)
+        branch.zero_()
+        self.mixer.forward(x, ctx, branch, cache)
+        x = self._close(branch, self.mixer_norm, hidden, ctx, n, width)
+        if self.ffn is not None:
+            branch.zero_()
+            self.ffn.forward(x, ctx, branch)
+            x = self._close(branch, self.ffn_norm, hidden, ctx, n, width)
+        ctx.hidden_copy = x if self.dtype != torch.float32 else None
+
+
 BLOCKS.register("prenorm", PreNormBlock)
+BLOCKS.register("branch_norm", BranchNormBlock)
 BLOCKS.register("parallel", ParallelBlock)

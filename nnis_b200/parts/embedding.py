@@ -58,10 +58,12 @@ class NormedTokenEmbedding(TokenEmbedding):
 
 
 class LinearHead(Part):
-    """params: vocab_size, hidden_size, name, tied_to (tensor stem or None)."""
+    """params: vocab_size, hidden_size, name, tied_to (tensor stem or None), softcap
+    (0: none; else logits <- softcap * tanh(logits / softcap), which changes no greedy pick)."""
 
     def __init__(self, params, prefix, dtype, device):
         super().__init__(params, prefix, dtype, device)
+        self.softcap = float(params.get("softcap") or 0.0)
         self.vocab = int(params["vocab_size"])
         self.width = int(params["hidden_size"])
         tied = params.get("tied_to")
@@ -85,6 +87,8 @@ class LinearHead(Part):
     def forward(self, x: torch.Tensor, logits: torch.Tensor) -> None:
         # (few rows: the decode projection kernel where it takes the shape)
         linear(x, self.weight, None, logits, STORE_F32, decode=True)
+        if self.softcap:
+            ops.softcap_rows(logits, self.softcap)
 
     def fuses_norm(self, norm, rows: int) -> bool:
         return (getattr(norm, "kind", None) == "rmsnorm" and self.dtype == torch.bfloat16
@@ -100,6 +104,8 @@ class LinearHead(Part):
         ops.gemv_bf16(self.weight, None, picks, ops.EPI_ARGMAX, hidden=hidden,
                       norm_weight=norm.weight, eps=norm.eps, rows=rows, m=picks.numel(),
                       logits=logits, scratch=scratch, next_tokens=next_tokens, next_pos=next_pos)
+        if self.softcap and logits is not None:
+            ops.softcap_rows(logits, self.softcap)
 
     def pick_scratch_ints(self, rows: int) -> int:
         return ops.argmax_scratch_ints(rows, self.vocab, self.width, self.device)
@@ -109,6 +115,8 @@ class LinearHead(Part):
         """Final norm of the wanted rows folded into the head (few rows)."""
         ops.gemv_bf16(self.weight, None, logits, ops.EPI_STORE_F32, hidden=hidden,
                       norm_weight=norm.weight, eps=norm.eps, rows=rows, m=logits.shape[0])
+        if self.softcap:
+            ops.softcap_rows(logits, self.softcap)
 
 
 EMBEDDINGS.register("token_embedding", TokenEmbedding)

@@ -5,8 +5,11 @@ at load) with float32 output; the activation kernel rounds once to the operand
 dtype.  Steps 14-18 of NNIS's token pass
 (crates/nnis-model/src/runtime.rs:1054-1093).
 
-params: hidden_size, intermediate_size, activation ("silu"), bias,
-names {gate, up, down}.
+params: hidden_size, intermediate_size, activation, bias, names {gate, up, down}.
+Activations: "silu" (silu(gate) * up, fused into the products' epilogues where those
+exist) and "glu_clamp" with ``limit`` and ``alpha``: g' sigmoid(alpha g') (u' + 1) with
+g' = min(gate, limit), u' = up clamped to [-limit, limit] (a kernel of its own after the
+float32 product).
 """
 from __future__ import annotations
 
@@ -27,8 +30,13 @@ class GatedMLP(Part):
         self.inter = int(params["intermediate_size"])
         self.bias = bool(params.get("bias", False))
         self.names = params["names"]
-        if params.get("activation", "silu") != "silu":
+        self.activation = params.get("activation", "silu")
+        if self.activation not in ("silu", "glu_clamp"):
             raise ValueError(f"gated_mlp: activation {params['activation']!r} has no kernel")
+        self.limit = float(params.get("limit", 0.0))
+        self.alpha = float(params.get("alpha", 1.0))
+        if self.activation == "glu_clamp" and not self.limit > 0:
+            raise ValueError("gated_mlp: glu_clamp needs a positive limit")
         self.w_gu = self.b_gu = self.w_down = self.b_down = None
 
     def weight_specs(self) -> Dict[str, WeightSpec]:
@@ -61,7 +69,7 @@ class GatedMLP(Part):
 
     def _fused_gate_up(self, ctx, n: int, normed: bool = False) -> bool:
         """The fused bfloat16 decode kernel for gate/up (few rows, one token each)."""
-        return (self.dtype == torch.bfloat16 and ctx.decode
+        return (self.dtype == torch.bfloat16 and ctx.decode and self.activation == "silu"
                 and ops.gemv_pays(n, 2 * self.inter, self.hidden, ops.EPI_GATED, self.device, normed))
 
     def _fused_down(self, ctx, n: int) -> bool:
@@ -74,6 +82,7 @@ class GatedMLP(Part):
     def shares_norm(self, norm, ctx, n: int) -> bool:
         """Whether gate/up can end a norm that the projection before it began."""
         return (getattr(norm, "kind", None) == "rmsnorm" and self.dtype == torch.bfloat16 and ctx.decode
+                and self.activation == "silu"
                 and ops.gemv_shares_norm(n, 2 * self.inter, self.hidden, ops.EPI_GATED, self.device))
 
     def forward(self, x: torch.Tensor, ctx, residual: torch.Tensor) -> None:
@@ -98,13 +107,17 @@ class GatedMLP(Part):
             ops.gemv_bf16(self.w_gu, self.b_gu, act, ops.EPI_GATED, x=x, hidden=hidden,
                           norm_weight=norm.weight if norm is not None else None,
                           eps=norm.eps if norm is not None else 0.0, m=n)
-        elif self.dtype == torch.bfloat16 and ops.gemm_tc_takes(n, 2 * self.inter, self.hidden):
+        elif self.activation == "silu" and self.dtype == torch.bfloat16 \
+                and ops.gemm_tc_takes(n, 2 * self.inter, self.hidden):
             # tensor-core product with the activation in its epilogue
             ops.gemm_tc(x, self.w_gu, self.b_gu, act, ops.GEMM_GATED)
         else:
             gate_up = ws.get("gate_up", (n, 2 * self.inter), torch.float32)
-            linear(x, self.w_gu, self.b_gu, gate_up, STORE_F32)
-            ops.silu_mul(gate_up, act)
+            linear(x, self.w_gu, self.b_gu, gate_up, STORE_F32, decode=ctx.decode)
+            if self.activation == "silu":
+                ops.silu_mul(gate_up, act)
+            else:
+                ops.glu_clamp(gate_up, act, self.limit, self.alpha)
         if self._fused_down(ctx, n):
             ops.gemv_bf16(self.w_down, self.b_down, residual, ops.EPI_ADD_F32, x=act,
                           emit=begin_norm(ctx, n, self.hidden))

@@ -16,9 +16,16 @@ run two grouped products on the tensor cores: the tcgen05 kernel of the dense pr
 with one weight matrix per tile of 128 rows where an expert gets many rows, 64 x 64
 mma.sync tiles where it gets few.
 
+A second form (``activation`` "silu_gated"): the expert is W_down (silu(W_gate x) * (W_up x))
+with x = score * h: the router's scores are sigmoid(z) (``scores`` "sigmoid"), used as they
+are, and they multiply the expert's INPUT (``weight_on`` "input"); the output is the plain sum
+of the chosen experts'.  Gate and up are stacked per expert ([experts, 2 ff, width]); the score
+multiplies their float32 sums, which is the product with score * h.
+
 params: hidden_size, experts, top, ff, shared_ff (0: no shared expert), activation
-("relu2"), names {router, router_bias, expert (a format with {e}), up, down,
-shared_up, shared_down, shared_gate}.
+("relu2" | "silu_gated"), scores ("softmax" over the chosen logits | "sigmoid"), weight_on
+("output" | "input"), names {router, router_bias (optional), expert (a format with {e}), up,
+down, gate (gated experts), shared_up, shared_down, shared_gate}.
 """
 from __future__ import annotations
 
@@ -44,8 +51,16 @@ class MoEFeedForward(Part):
         self.ff = int(params["ff"])
         self.shared_ff = int(params.get("shared_ff") or 0)
         self.names = params["names"]
-        if params.get("activation", "relu2") != "relu2":
-            raise ValueError(f"moe: activation {params['activation']!r} has no kernel")
+        self.activation = params.get("activation", "relu2")
+        self.scores = params.get("scores", "softmax")
+        self.weight_on = params.get("weight_on", "output")
+        if (self.activation, self.scores, self.weight_on) not in (("relu2", "softmax", "output"),
+                                                                  ("silu_gated", "sigmoid", "input")):
+            raise ValueError(f"moe: no kernel for activation {self.activation!r} with {self.scores!r} scores "
+                             f"on the expert's {self.weight_on}")
+        self.gated = self.activation == "silu_gated"
+        if self.gated and self.shared_ff:
+            raise ValueError("moe: the gated form has no shared expert")
         if not 0 < self.top <= self.experts:
             raise ValueError(f"moe: top={self.top} of {self.experts} experts")
         self.w_router = self.b_router = self.w_up = self.w_down = None
@@ -57,9 +72,12 @@ class MoEFeedForward(Part):
     def weight_specs(self) -> Dict[str, WeightSpec]:
         W = self.hidden
         # the router is held in float32 whatever the operand dtype ("vector": kept as float32)
-        specs = {self.tensor_name(self.names["router"]): WeightSpec((self.experts, W), "vector", fan_in=W),
-                 self.tensor_name(self.names["router_bias"]): WeightSpec((self.experts,), "vector")}
+        specs = {self.tensor_name(self.names["router"]): WeightSpec((self.experts, W), "vector", fan_in=W)}
+        if self.names.get("router_bias"):
+            specs[self.tensor_name(self.names["router_bias"])] = WeightSpec((self.experts,), "vector")
         for e in range(self.experts):
+            if self.gated:
+                specs[self._expert(e, "gate")] = WeightSpec((self.ff, W), "matrix", fan_in=W)
             specs[self._expert(e, "up")] = WeightSpec((self.ff, W), "matrix", fan_in=W)
             specs[self._expert(e, "down")] = WeightSpec((W, self.ff), "matrix", fan_in=self.ff)
         if self.shared_ff:
@@ -71,8 +89,13 @@ class MoEFeedForward(Part):
 
     def load(self, tensors: Mapping[str, torch.Tensor]) -> None:
         self.w_router = tensors[self.tensor_name(self.names["router"])]
-        self.b_router = tensors[self.tensor_name(self.names["router_bias"])]
-        self.w_up = torch.stack([tensors[self._expert(e, "up")] for e in range(self.experts)]).contiguous()
+        self.b_router = tensors[self.tensor_name(self.names["router_bias"])] \
+            if self.names.get("router_bias") else None
+        if self.gated:  # gate rows, then up rows, per expert
+            self.w_up = torch.stack([torch.cat([tensors[self._expert(e, "gate")], tensors[self._expert(e, "up")]], 0)
+                                     for e in range(self.experts)]).contiguous()
+        else:
+            self.w_up = torch.stack([tensors[self._expert(e, "up")] for e in range(self.experts)]).contiguous()
         self.w_down = torch.stack([tensors[self._expert(e, "down")] for e in range(self.experts)]).contiguous()
         if self.shared_ff:
             up = tensors[self.tensor_name(self.names["shared_up"])]
@@ -85,7 +108,7 @@ class MoEFeedForward(Part):
 
     def parameter_bytes(self) -> int:
         """What a step of one token reads: the router, ``top`` experts, the shared one."""
-        per_expert = 2 * self.ff * self.hidden * self.w_up.element_size()
+        per_expert = (3 if self.gated else 2) * self.ff * self.hidden * self.w_up.element_size()
         shared = sum(t.numel() * t.element_size() for t in (self.w_shared_up, self.w_shared_down)
                      if t is not None)
         return self.w_router.numel() * 4 + self.top * per_expert + shared
@@ -94,13 +117,14 @@ class MoEFeedForward(Part):
         """Bytes of weights that a step of ``rows`` tokens reads when the router spreads them
         evenly: the experts that at least one token chooses (experts * (1 - (1 - top / experts)
         ^ rows) of them in expectation), the router and the shared expert."""
-        per_expert = 2 * self.ff * self.hidden * self.w_up.element_size()
+        per_expert = (3 if self.gated else 2) * self.ff * self.hidden * self.w_up.element_size()
         chosen = self.experts * (1.0 - (1.0 - self.top / self.experts) ** max(1, rows))
         return int(self.parameter_bytes() + (chosen - self.top) * per_expert)
 
     def step_flops(self, counts, starts) -> float:
         W = self.hidden
-        per_token = W * self.experts + 2 * self.top * self.ff * W + self.shared_ff * (2 * W + 1) + W
+        per_token = W * self.experts + (3 if self.gated else 2) * self.top * self.ff * W \
+            + self.shared_ff * (2 * W + 1) + W
         return 2.0 * sum(counts) * per_token
 
     def forward(self, x: torch.Tensor, ctx, residual: torch.Tensor) -> None:
@@ -108,7 +132,12 @@ class MoEFeedForward(Part):
         ws = ctx.workspace
         ids = ws.get("moe_ids", (n, self.top), torch.int32)
         weights = ws.get("moe_weights", (n, self.top), torch.float32)
-        ops.moe_route(x, self.w_router, self.b_router, ctx.token_pos, ids, weights, self.top)
+        ops.moe_route(x, self.w_router, self.b_router, ctx.token_pos, ids, weights, self.top,
+                      sigmoid_scores=self.scores == "sigmoid")
+        if self.gated:
+            act = ws.get("moe_act", (n, self.top, self.ff), self.dtype)
+            ops.moe_experts_gated(x, self.w_up, self.w_down, ids, weights, ctx.token_pos, act, residual, self.top)
+            return
         grouped = self.dtype == torch.bfloat16 and not ctx.decode and n >= self.GROUPED_FROM \
             and ops.moe_grouped_takes(self.hidden, self.ff, self.experts)
         if grouped and ops.TC_GEMM and n * self.top >= self.TCGEN05_ROWS * self.experts:

@@ -7,6 +7,7 @@ angle = position * inv_f.  ``none`` leaves heads as they are.
 """
 from __future__ import annotations
 
+import math
 from typing import Dict, Optional, Tuple
 
 import torch
@@ -40,25 +41,52 @@ class RotaryHalf(PositionEncoding):
 
 
 class RotaryFrequencies(PositionEncoding):
-    """Rotate-half rotation of the first ``dims`` of a vector by angles position *
-    base^(-2i/dims), i = 0 .. dims/2 - 1, with the angle and its cosine and sine
+    """Rotation of the first ``dims`` of a vector by angles position * f_i,
+    f_i = base^(-2i/dims), i = 0 .. dims/2 - 1, with the angle and its cosine and sine
     computed in float32 inside the kernels from a table of the ``dims / 2`` frequencies:
-    no table of positions, so no bound on them.  params: dims, base.  Mixers whose
-    kernels take frequencies (latent attention, retention) ask for ``frequencies()``."""
+    no table of positions, so no bound on them.  params: dims, base, and optionally
+    ``pairing`` ("half": value i turns with value i + dims/2, the rule; "neighbours":
+    value 2i with value 2i + 1; the mixer's kernel has to know the pairing it is given)
+    and ``scaling`` {factor, low, high, original}: frequencies whose wavelength 2 pi / f
+    exceeds original / low are divided by ``factor``, those with a wavelength below
+    original / high stay, and between the two the frequency is (1 - s) f / factor + s f
+    with s = (original / wavelength - low) / (high - low).  Mixers whose kernels take
+    frequencies (latent attention, retention, attention with a sink) ask for ``frequencies()``."""
 
     def __init__(self, params, prefix, dtype, device):
         super().__init__(params, prefix, dtype, device)
         self.dims = int(params["dims"])
         self.base = float(params["base"])
+        self.pairing = params.get("pairing", "half")
+        self.scaling = params.get("scaling")
         if self.dims < 0 or self.dims % 2:
             raise ValueError(f"rotation: dims={self.dims} must be even")
+        if self.pairing not in ("half", "neighbours"):
+            raise ValueError(f"rotation: pairing {self.pairing!r} is not known (half, neighbours)")
+        if self.scaling is not None:
+            sc = self.scaling
+            if not all(float(sc[k]) > 0 for k in ("factor", "low", "high", "original")) \
+                    or float(sc["high"]) == float(sc["low"]):
+                raise ValueError("rotation: scaling needs positive factor, low, high, original and low != high")
         self._freq: Optional[torch.Tensor] = None
+
+    def _scaled(self, freq: torch.Tensor) -> torch.Tensor:
+        sc = self.scaling
+        factor, low, high, original = (float(sc[k]) for k in ("factor", "low", "high", "original"))
+        f = freq.to(torch.float64)
+        wavelength = 2.0 * math.pi / f
+        s = (original / wavelength - low) / (high - low)
+        between = (1.0 - s) * f / factor + s * f
+        out = torch.where(wavelength < original / high, f, torch.where(wavelength > original / low, f / factor, between))
+        return out.to(torch.float32)
 
     def frequencies(self) -> torch.Tensor:
         if self._freq is None:
             half = self.dims // 2
-            exponent = -(2 * torch.arange(half, dtype=torch.float32)) / float(max(self.dims, 1))
-            freq = torch.pow(torch.tensor(self.base, dtype=torch.float32), exponent)
+            exponent = -(2 * torch.arange(half, dtype=torch.float64)) / float(max(self.dims, 1))
+            freq = torch.pow(torch.tensor(self.base, dtype=torch.float64), exponent).to(torch.float32)
+            if self.scaling is not None and half:
+                freq = self._scaled(freq)
             # (one spare entry so that dims == 0 still has an address)
             self._freq = torch.cat([freq, torch.zeros(1)]).to(self.device).contiguous()
         return self._freq

@@ -39,10 +39,16 @@ class WeightError(ValueError):
 
 @dataclass(frozen=True)
 class WeightSpec:
-    shape: Tuple[int, ...]
+    shape: Tuple[int, ...]  # an extent of -1: whatever the stored tensor has there
     role: str  # "matrix" | "vector" | "table" (integer)
     init: str = "normal"  # random mode: "normal" around 0, "ones" around 1
     fan_in: int = 0  # random mode: inputs summed per output (0: not a projection)
+
+
+def shape_fits(shape, wanted) -> bool:
+    """Whether a stored shape is the wanted one; -1 in ``wanted`` leaves an extent free (a size
+    that the configuration does not name and the tensor itself gives)."""
+    return len(shape) == len(wanted) and all(w == -1 and s > 0 or s == w for s, w in zip(shape, wanted))
 
 
 def _discover(model_dir: str) -> List[str]:
@@ -116,7 +122,7 @@ def _open_and_check(model_dir: str, wanted: Mapping[str, WeightSpec]):
             if name not in where:
                 continue
             dtype, shape = where[name].meta(name)
-            if tuple(shape) != tuple(spec.shape):
+            if not shape_fits(shape, spec.shape):
                 wrong.append(f"{name}: shape {list(shape)}, expected {list(spec.shape)}")
             elif spec.role == "table" and dtype.is_floating_point:
                 wrong.append(f"{name}: dtype {dtype}, expected an integer type")
