@@ -1481,6 +1481,35 @@ def attention_sink(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor
                                       _stream()), "attention_sink", 2 if n_splits > 1 else 1)
 
 
+def attention_sink_mma_takes(dk: int, dv: int, page_size: int) -> bool:
+    """Whether the tensor-core prompt form of the sink attention takes these head sizes."""
+    return dk == dv and dk in (64, 128) and page_size == 64
+
+
+def attention_sink_mma(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, tiles: torch.Tensor,
+                       seq_first_row: torch.Tensor, seq_start: torch.Tensor, seq_count: torch.Tensor,
+                       page_table: torch.Tensor, sink: Optional[torch.Tensor], gate: Optional[torch.Tensor],
+                       out: torch.Tensor, heads: int, kv_heads: int, window: int, chunk: int, scale: float,
+                       cap: float) -> None:
+    """``attention_sink`` for prompt steps in bfloat16 on mma.sync tiles; ``tiles`` int32 [n, 2] =
+    (sequence, first query) per 64 queries."""
+    _cuda(q, k_cache, v_cache, tiles, seq_first_row, seq_start, seq_count, page_table, sink, gate, out)
+    pages, nkv, page_size, d = k_cache.shape
+    n = out.shape[0]
+    _need(q.dtype == k_cache.dtype == v_cache.dtype == out.dtype == torch.bfloat16, "attention_sink_mma: bfloat16")
+    _need(attention_sink_mma_takes(d, v_cache.shape[3], page_size) and nkv == kv_heads,
+          "attention_sink_mma: heads of 64 or 128 for keys and values alike, pages of 64")
+    _need(tuple(q.shape) == tuple(out.shape) == (n, heads * d), "attention_sink_mma: q, out [n, heads * d]")
+    _need(tiles.dtype == torch.int32 and tiles.dim() == 2 and tiles.shape[1] == 2, "attention_sink_mma: tiles [n, 2]")
+    _need(sink is None or (sink.dtype == torch.float32 and sink.numel() == heads), "attention_sink_mma: sink")
+    _need(gate is None or (gate.dtype == torch.float32 and gate.numel() >= n * heads), "attention_sink_mma: gate")
+    _check(_lib().nnis_attention_sink_mma(_ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(tiles), tiles.shape[0],
+                                          _ptr(seq_first_row), _ptr(seq_start), _ptr(seq_count), _ptr(page_table),
+                                          page_table.shape[1], _ptr(sink), _ptr(gate), _ptr(out), heads, kv_heads, d,
+                                          page_size, window, chunk, ctypes.c_float(scale), ctypes.c_float(cap),
+                                          _stream()), "attention_sink_mma")
+
+
 def moe_experts_gated(h: torch.Tensor, w_gu: torch.Tensor, w_down: torch.Tensor, ids: torch.Tensor,
                       weights: torch.Tensor, token_pos: torch.Tensor, act: torch.Tensor,
                       residual: torch.Tensor, top: int) -> None:

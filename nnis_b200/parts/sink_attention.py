@@ -20,7 +20,8 @@ Keys (after norm and rotation) and values live in the cache; with ``kv == "share
 part has no k/v projection, norm or cache of its own and reads another schedule entry's.
 One projection makes q, k, v and the gate's logits in float32 (their matrices are
 stacked at load); ``qkv_prep`` norms, rotates, stores and takes the sigmoid; the attention
-kernel serves prompts, later portions and single tokens alike.
+kernel serves prompts, later portions and single tokens alike; prompt steps in bfloat16 with
+key and value heads of 64 or 128 run a tensor-core form of it (``attention_sink_mma``).
 
 params: hidden_size, heads, kv_heads, dim, vdim, scale, softcap, chunk, window, sink,
 gate, qk_norm, eps, position (a ``rope_frequencies`` PartSpec with neighbouring pairs),
@@ -30,9 +31,10 @@ from __future__ import annotations
 
 from typing import Dict, Mapping, Optional
 
+import numpy as np
 import torch
 
-from ..cache import KVRequest, KVView
+from ..cache import PAGE_SIZE, KVRequest, KVView
 from ..csrc import ops
 from ..weights.loader import WeightSpec
 from .base import MIXERS, POSITIONS, Part
@@ -131,6 +133,19 @@ class SinkAttention(Part):
             flops += 2.0 * H * (self.dim + self.vdim) * keys
         return flops
 
+    # -- work lists ---------------------------------------------------------
+    TILES_64 = "prefill_mma/tiles64"  # (sequence, first query) per 64 queries of the step
+
+    def _mma_prompt(self) -> bool:
+        return self.dtype == torch.bfloat16 and ops.attention_sink_mma_takes(self.dim, self.vdim, PAGE_SIZE)
+
+    def step_tables(self, counts, starts, have=()):
+        """The 64-query tiles of the tensor-core prompt kernel (the same list for every layer)."""
+        if not self._mma_prompt() or self.TILES_64 in have:
+            return {}
+        tiles = [(i, q0) for i, c in enumerate(counts) for q0 in range(0, int(c), 64)]
+        return {self.TILES_64: np.asarray(tiles, dtype=np.int32).reshape(-1, 2)}
+
     # -- run --------------------------------------------------------------
     def forward(self, x: torch.Tensor, ctx, residual: torch.Tensor, cache: KVView) -> None:
         n = residual.shape[0]
@@ -144,6 +159,12 @@ class SinkAttention(Part):
                      table if G else None, q, cache.k if G else None, cache.v if G else None, gate, H, G,
                      self.dim, self.vdim, self.position.dims, self.eps)
         out = ws.get("sink_attention_out", (n, H * self.vdim), self.dtype)
+        if not ctx.decode and self._mma_prompt() and self.TILES_64 in ctx.tables:
+            ops.attention_sink_mma(q, cache.k, cache.v, ctx.tables[self.TILES_64], ctx.seq_first_row, ctx.seq_start,
+                                   ctx.seq_count, table, self.sink, gate, out, H, self.kv_heads, self.window,
+                                   self.chunk, self.scale, self.softcap)
+            linear(out, self.w_o, None, residual, ADD_F32, ws, decode=ctx.decode)
+            return
         splits = ctx.attention_splits(n * H)
         partial = ws.get("attn_partial", (n * H * splits * (self.vdim + 2),), torch.float32) if splits > 1 else None
         ops.attention_sink(q, cache.k, cache.v, ctx.token_pos, ctx.token_seq, table, self.sink, gate, out, H,

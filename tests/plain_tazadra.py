@@ -2,9 +2,9 @@
 mechanism, written from the design's equations.  It reads config.json's keys and the
 tensor names by itself and shares no code with the package.
 
-``emulate_bf16`` rounds where the bfloat16 engine rounds (projections' inputs and
-outputs, cached keys and values, activations); norms, scores, softmax, routers,
-recurrences and the residual sum stay exact.
+``emulate_bf16`` rounds where the bfloat16 engine rounds (projections' inputs, the outputs
+that feed another projection or the cache, activations); norms, scores, softmax, routers,
+recurrences, what enters them, and the residual sum stay exact.
 """
 from __future__ import annotations
 
@@ -77,22 +77,21 @@ def attention_keys_values(h, w, p, m, eps, positions, e16):
     projection and the rotation, and values."""
     G, d, dv = m["kv_heads"], m["dim"], m["vdim"]
     T = h.shape[0]
-    k = bf(h @ w[p + ".k"].T, e16)
+    k = h @ w[p + ".k"].T
     v = bf(h @ w[p + ".v"].T, e16)
     k = rms_norm(k, w[p + ".k.norm"], eps).reshape(T, G, d)
     k = bf(rotate_pairs(k, positions, frequencies(m["rot"])), e16)
     return k, v.reshape(T, G, dv)
 
 
-def attention(h, w, p, m, eps, positions, keys, values, e16):
+def attention(h, w, p, m, eps, positions, keys, values, e16, probes: Optional[dict] = None):
     """h [T, width] -> [T, width]; keys [T, G, d], values [T, G, dv] of the same positions
     (its own, or those of the layer that ``kv_from`` names)."""
     H, G, d, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
     T = h.shape[0]
-    q = bf(h @ w[p + ".q"].T, e16)
-    q = rms_norm(q, w[p + ".q.norm"], eps).reshape(T, H, d)
+    q = rms_norm(h @ w[p + ".q"].T, w[p + ".q.norm"], eps).reshape(T, H, d)
     q = bf(rotate_pairs(q, positions, frequencies(m["rot"])), e16)
-    gate = torch.sigmoid(bf(h @ w[p + ".g"].T, e16))  # [T, H]
+    gate = torch.sigmoid(h @ w[p + ".g"].T)  # [T, H]
     out = torch.zeros(T, H, dv, dtype=F)
     chunk = int(m["mask"]["size"]) if m.get("mask") else 0
     cap = float(m.get("softcap") or 0.0)
@@ -111,7 +110,10 @@ def attention(h, w, p, m, eps, positions, keys, values, e16):
         e = torch.exp(s - top[:, None])
         denom = e.sum(dim=1) + torch.exp(sink - top)
         out[:, hq] = (e / denom[:, None]) @ values[:, g]
-    out = bf(out, e16) * gate[:, :, None]
+        if probes is not None:  # [heads, T, T] softmax weights, and the sink's share [heads, T]
+            probes.setdefault("weights", []).append(e / denom[:, None])
+            probes.setdefault("sink", []).append(torch.exp(sink - top) / denom)
+    out = out * gate[:, :, None]
     return bf(out.reshape(T, H * dv), e16) @ w[p + ".o"].T
 
 
@@ -127,8 +129,8 @@ def wkv(h, w, p, m, eps, e16):
     k = bf(mix("k") @ w[p + ".k"].T, e16).reshape(T, H, d)
     v = bf(mix("v") @ w[p + ".v"].T, e16).reshape(T, H, d)
     gate = silu(bf(mix("g") @ w[p + ".g"].T, e16))
-    low = torch.tanh(bf(mix("w") @ w[p + ".w1"].T, e16))
-    decay = torch.exp(-torch.exp(bf(low, e16) @ w[p + ".w2"].T + w[p + ".w0"])).reshape(T, H, d)
+    low = bf(torch.tanh(mix("w") @ w[p + ".w1"].T), e16)
+    decay = torch.exp(-torch.exp(low @ w[p + ".w2"].T + w[p + ".w0"])).reshape(T, H, d)
     u = w[p + ".u"].reshape(H, d)
     out = torch.zeros(T, H, d, dtype=F)
     S = torch.zeros(H, d, d, dtype=F)  # [head, key channel, value channel]
@@ -150,8 +152,8 @@ def mamba1(h, w, p, m, e16):
     conv = w[p + ".conv"]  # [inner, taps], the last column is the current token's
     x = sum(padded[j:j + T] * conv[:, j] for j in range(taps)) + w[p + ".conv.b"]
     x = bf(silu(x), e16)
-    dbc = bf(x @ w[p + ".x"].T, e16)
-    dt, B, C = dbc[:, :R], dbc[:, R:R + N], dbc[:, R + N:]
+    dbc = x @ w[p + ".x"].T
+    dt, B, C = bf(dbc[:, :R], e16), dbc[:, R:R + N], dbc[:, R + N:]
     dt = softplus(dt @ w[p + ".dt"].T + w[p + ".dt.b"])  # [T, inner]
     A = -torch.exp(w[p + ".A_log"])  # [inner, N]
     S = torch.zeros(inner, N, dtype=F)
@@ -188,7 +190,7 @@ def moe_ff(h, w, p, mlp, e16, margins: Optional[List] = None):
     out = torch.zeros_like(h)
     for t in range(h.shape[0]):
         for e, s in zip(ids[t].tolist(), val[t]):
-            x = bf(h[t] * s, e16)
+            x = h[t] * s  # (a scalar on the input: the engine applies it to the two products' sums)
             a = silu(x @ w[f"{p}.e{e}.gate"].T) * (x @ w[f"{p}.e{e}.up"].T)
             out[t] += bf(a, e16) @ w[f"{p}.e{e}.down"].T
     return out
@@ -196,7 +198,8 @@ def moe_ff(h, w, p, mlp, e16, margins: Optional[List] = None):
 
 # ---- the model ----------------------------------------------------------------------------
 def forward(cfg: dict, w: Dict[str, torch.Tensor], tokens, emulate_bf16: bool = False,
-            margins: Optional[List] = None, layers_out: Optional[List] = None) -> torch.Tensor:
+            margins: Optional[List] = None, layers_out: Optional[List] = None,
+            probes: Optional[Dict[int, dict]] = None) -> torch.Tensor:
     """Logits [T, vocab] of one sequence from its first token."""
     w = {k: v.to(F) for k, v in w.items()}
     e16 = emulate_bf16
@@ -212,7 +215,8 @@ def forward(cfg: dict, w: Dict[str, torch.Tensor], tokens, emulate_bf16: bool = 
             if m.get("kv_from") is None:
                 kept[i] = attention_keys_values(h, w, p, m, eps, positions, e16)
             keys, values = kept[i if m.get("kv_from") is None else int(m["kv_from"])]
-            y = attention(h, w, p, m, eps, positions, keys, values, e16)
+            y = attention(h, w, p, m, eps, positions, keys, values, e16,
+                          probes.setdefault(i, {}) if probes is not None else None)
         elif layer["type"] == "wkv":
             y = wkv(h, w, p, m, eps, e16)
         elif layer["type"] == "mamba1":
@@ -231,3 +235,15 @@ def forward(cfg: dict, w: Dict[str, torch.Tensor], tokens, emulate_bf16: bool = 
     logits = bf(rms_norm(x, w["final.norm"], eps), e16) @ w["head"].T
     cap = float(cfg.get("logit_softcap") or 0.0)
     return cap * torch.tanh(logits / cap) if cap else logits
+
+
+def greedy_generate(cfg: dict, w: Dict[str, torch.Tensor], prompt, new_tokens: int) -> List[int]:
+    """The tokens that greedy decoding appends (ties to the lower id), the slow way: the
+    whole sequence again for every token."""
+    seq, out = list(prompt), []
+    for _ in range(new_tokens):
+        logits = forward(cfg, w, seq)[-1]
+        best = int(torch.nonzero(logits == logits.max())[0])
+        out.append(best)
+        seq.append(best)
+    return out
