@@ -3,7 +3,7 @@
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
                     [--shape 135m|360m|1.7b] [--batch B] [--context C] [--layers L] [--skip-points]
-                    [--skip-e2e] [--designs s,m]
+                    [--skip-e2e] [--designs s,m [--only-design llama,nafezen,tazadra]]
 
 A step is one decode step of a batch of 8 sequences whose context ends at 4,096
 tokens (prompt 2,048 + 2,048 decoded); ``value`` is decoded tokens per second,
@@ -236,12 +236,14 @@ def timeline(engine, batch, path, rng, vocab):
 
 
 # ---------------------------------------------------------------------------
-# --designs: the Nafezen design beside the Llama decoder at equal width and depth
+# --designs: the Nafezen and Tazadra designs beside the Llama decoder at equal width and depth
 # ---------------------------------------------------------------------------
 def design_configs(size: str):
-    """(Llama config, Nafezen config) of one width, depth and feed-forward size; the Nafezen
-    layers alternate latent attention with dense and expert feed-forwards and hold one
-    retention layer in four."""
+    """(Llama, Nafezen, Tazadra) configurations of one width, depth, vocabulary and dense
+    feed-forward size; the Nafezen layers alternate latent attention with dense and expert
+    feed-forwards and hold one retention layer in four; the Tazadra layers are attention with a
+    sink + dense, WKV + experts, selective scan + experts, and attention that reads the first
+    layer's keys + dense, twice."""
     width, heads, ff, layers, q_rank, kv_rank, experts, top = {
         "s": (1024, 16, 2816, 8, 384, 256, 16, 2),
         "m": (2048, 16, 5632, 8, 768, 512, 32, 4),
@@ -264,7 +266,25 @@ def design_configs(size: str):
                ("retention", retention, moe), ("latent_attention", latent, dense)]
     nafezen = {"architecture": "Nafezen", "vocab": 32768, "width": width, "norm": {"eps": 1e-5, "groups": 4},
                "layers": [{"type": t, "mixer": m, "mlp": f} for t, m, f in (pattern[i % 4] for i in range(layers))]}
-    return llama, nafezen
+    attention = {"heads": heads, "kv_heads": heads // 4, "dim": dim, "vdim": dim, "scale": dim ** -0.5,
+                 "softcap": 30.0, "mask": {"size": 1024},
+                 "rot": {"base": 100000.0, "dims": dim,
+                         "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 1024}}}
+    wkv = {"heads": width // 64, "dim": 64, "decay_rank": 64}
+    scan = {"inner": 2 * width, "state": 16, "dt_rank": width // 16, "conv": 4}
+    t_dense = {"kind": "dense", "ff": ff, "limit": 7.0}
+    t_moe = {"kind": "moe", "router": {"experts": experts, "top": top}, "expert": {"ff": ff // (2 * top)}}
+    t_layers = []
+    for i in range(layers):
+        kind, mixer, mlp = [("attention", attention, t_dense), ("wkv", wkv, t_moe), ("mamba1", scan, t_moe),
+                            ("attention", {**attention, "kv_from": i - 3}, t_dense)][i % 4]
+        t_layers.append({"type": kind, "mixer": mixer, "mlp": mlp})
+    tazadra = {"architecture": "Tazadra", "vocab": 32768, "width": width, "norm": {"eps": 1e-5},
+               "residual_mult": 0.5, "logit_softcap": 30.0, "layers": t_layers}
+    return llama, nafezen, tazadra
+
+
+DESIGN_NAMES = ("llama", "nafezen", "tazadra")
 
 
 def profile_steps(args) -> int:
@@ -277,7 +297,7 @@ def profile_steps(args) -> int:
     from nnis_b200.engine import Engine, SequenceStep
     from nnis_b200.weights import write_random_model
     engine_module.GRAPH_MIN_TOKENS = 1 << 30
-    _, cfg = design_configs(args.designs.split(",")[0])
+    cfg = design_configs(args.designs.split(",")[0])[DESIGN_NAMES.index(args.profile_design)]
     cfg["layers"] = cfg["layers"][:4]
     rng = random.Random(0)
     with tempfile.TemporaryDirectory() as tmp:
@@ -293,7 +313,7 @@ def profile_steps(args) -> int:
     for _ in range(args.profile_steps):
         engine.step([SequenceStep(s, [5], [0]) for s in slots])
     torch.cuda.synchronize()
-    print(json.dumps({"profile_steps": args.profile_steps, "layers": 4, "design": "nafezen"}))
+    print(json.dumps({"profile_steps": args.profile_steps, "layers": 4, "design": args.profile_design}))
     return 0
 
 
@@ -327,7 +347,9 @@ def compare_designs(args) -> int:
         return start.elapsed_time(end) / n
 
     for size in args.designs.split(","):
-        for name, cfg in zip(("llama", "nafezen"), design_configs(size)):
+        for name, cfg in zip(DESIGN_NAMES, design_configs(size)):
+            if args.only_design and name not in args.only_design.split(","):
+                continue
             with tempfile.TemporaryDirectory() as tmp:
                 write_random_model(cfg, seed=0, out_dir=tmp, std=1.0, norm_std=0.1, std_by_fan_in=True)
                 llm = LLM(tmp, dtype="bfloat16", device_ordinal=0, max_tokens=batch * (context + 64) + 4 * prompt_len,
@@ -447,11 +469,15 @@ def main() -> int:
     ap.add_argument("--shape", default="135m", choices=sorted(SHAPES),
                     help="layer sizes: the SmolLM2-135M shape (the benchmark) or a larger one of the family")
     ap.add_argument("--designs", metavar="SIZES", default=None,
-                    help="instead of the benchmark: the Nafezen design beside the Llama decoder at equal "
-                         "width and depth, sizes 's' and/or 'm' with commas: prefill, its parts, decoding")
+                    help="instead of the benchmark: the Nafezen and Tazadra designs beside the Llama decoder at "
+                         "equal width and depth, sizes 's' and/or 'm' with commas: prefill, its parts, decoding")
+    ap.add_argument("--only-design", metavar="NAMES", default=None,
+                    help="with --designs: only these of llama, nafezen, tazadra (commas between them)")
     ap.add_argument("--profile-steps", type=int, default=0,
-                    help="with --designs: run this many eager prompt and decode steps of the Nafezen model "
-                         "for a profiler instead of the timed comparison")
+                    help="with --designs: run this many eager prompt and decode steps of one design's first "
+                         "four layers for a profiler instead of the timed comparison")
+    ap.add_argument("--profile-design", choices=list(DESIGN_NAMES), default="nafezen",
+                    help="with --profile-steps: which design")
     args = ap.parse_args()
     if args.designs:
         return profile_steps(args) if args.profile_steps > 0 else compare_designs(args)

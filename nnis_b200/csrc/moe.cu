@@ -17,8 +17,8 @@
 //                  the score multiplies both float32 sums, which is the product with w * h
 //   moe_down       with no weights: the chosen experts' outputs are added as they are
 //
-// Expert weights are stacked: W_up [experts, ff, width] (gated: [experts, 2 ff, width], gate rows
-// first), W_down [experts, width, ff].
+// Expert weights are stacked: W_up [experts, ff, width] (gated: [experts, 2 ff, width], row 2f the
+// gate's and row 2f + 1 the up-projection's of feature f), W_down [experts, width, ff].
 // A row whose position is -1 (padding) is skipped everywhere.
 #include <float.h>
 
@@ -149,8 +149,8 @@ moe_up_gated_kernel(const T* __restrict__ h, const T* __restrict__ w_gu, const i
     int f = blockIdx.y * 8 + warp;
     long long n = pair / top;
     if (f >= ff || token_pos[n] < 0) return;
-    const T* wg = w_gu + ((size_t)ids[pair] * 2 * ff + f) * width;
-    const T* wu = wg + (size_t)ff * width;
+    const T* wg = w_gu + ((size_t)ids[pair] * 2 * ff + 2 * f) * width;  // (rows interleaved: gate, up)
+    const T* wu = wg + width;
     const T* x = h + (size_t)n * width;
     float g = warp_row_dot(wg, x, width, lane);
     float u = warp_row_dot(wu, x, width, lane);
@@ -238,7 +238,8 @@ NNIS_API int nnis_moe_experts(const void* h, const void* w_up, const void* w_dow
     return e == cudaSuccess ? NNIS_OK : (int)e;
 }
 
-// The gated form: w_gu [experts, 2 ff, width]; the weights multiply the experts' inputs.
+// The gated form: w_gu [experts, 2 ff, width], gate and up rows interleaved; the weights multiply
+// the experts' inputs.
 NNIS_API int nnis_moe_experts_gated(const void* h, const void* w_gu, const void* w_down, const int* ids,
                                     const float* weights, const int* token_pos, void* act, float* residual,
                                     int n_tokens, int width, int ff, int top, int dtype, cudaStream_t stream) {

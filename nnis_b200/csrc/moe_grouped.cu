@@ -12,6 +12,11 @@
 //                 second reads the sorted activations and stores float32.
 //   moe_combine   residual[n] += sum_s weight[n, s] * y[place[n, s]], in the router's order
 //
+// Gated experts whose scores multiply their inputs (nnis_moe_grouped_gated): the gate's and the
+// up-projection's rows are interleaved in the stacked weights (row 2f the gate's, 2f + 1 the
+// up's), so a thread of the first product holds both sums of an output feature; it multiplies
+// them by the pair's score and stores silu(g) * u; the combine step then adds without weights.
+//
 // Where an expert gets many rows (nnis_moe_grouped_tc) the runs are padded to 128 rows
 // instead, moe_gather puts the tokens' inputs into the sorted order, and both products run
 // on the tcgen05 kernel of the dense projections with one weight matrix per tile of rows
@@ -77,7 +82,7 @@ __global__ void __launch_bounds__(128)
 grouped_mma_kernel(const bf16* __restrict__ a, int lda, const int* __restrict__ perm, int top,
                    const bf16* __restrict__ w, const int* __restrict__ tile_expert,
                    void* __restrict__ out, int N, int K, int M, long long a_bs, int ldc,
-                   long long c_bs) {
+                   long long c_bs, const float* __restrict__ pair_weight = nullptr) {
     constexpr int BK = 64, STAGES = 3, CH = BK / 8;
     const int expert = MODE == 2 ? (int)blockIdx.z : tile_expert[blockIdx.x];
     if (expert < 0) return;
@@ -86,6 +91,7 @@ grouped_mma_kernel(const bf16* __restrict__ a, int lda, const int* __restrict__ 
     bf16* a_s = reinterpret_cast<bf16*>(smem_raw);          // stages x [64, 64]
     bf16* w_s = a_s + STAGES * kGroupRows * BK;             // stages x [64, 64]
     __shared__ int src_row[kGroupRows];
+    __shared__ float row_weight[kGroupRows];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int row0 = blockIdx.x * kGroupRows, n0 = blockIdx.y * 64;
     if (tid < kGroupRows) {
@@ -93,7 +99,8 @@ grouped_mma_kernel(const bf16* __restrict__ a, int lda, const int* __restrict__ 
             src_row[tid] = row0 + tid < M ? row0 + tid : -1;
         } else {
             int p = perm[row0 + tid];
-            src_row[tid] = MODE == 0 ? (p < 0 ? -1 : p / top) : (p < 0 ? -1 : row0 + tid);
+            src_row[tid] = (MODE == 0 || MODE == 3) ? (p < 0 ? -1 : p / top) : (p < 0 ? -1 : row0 + tid);
+            if (MODE == 3) row_weight[tid] = p < 0 ? 0.f : pair_weight[p];
         }
     }
     __syncthreads();
@@ -156,6 +163,11 @@ grouped_mma_kernel(const bf16* __restrict__ a, int lda, const int* __restrict__ 
                 bf16* o = reinterpret_cast<bf16*>(out);
                 if (col < N) o[base + col] = __float2bfloat16_rn(v0);
                 if (col + 1 < N) o[base + col + 1] = __float2bfloat16_rn(v1);
+            } else if (MODE == 3) {  // (v0, v1) = (gate, up) of feature col / 2; the score on both
+                const float g = v0 * row_weight[r], u = v1 * row_weight[r];
+                bf16* o = reinterpret_cast<bf16*>(out);
+                if (col + 1 < N) o[(size_t)(row0 + r) * (N >> 1) + (col >> 1)] =
+                    __float2bfloat16_rn(g / (1.0f + __expf(-g)) * u);
             } else if (MODE == 0) {
                 v0 = fmaxf(v0, 0.f);
                 v1 = fmaxf(v1, 0.f);
@@ -191,8 +203,10 @@ moe_combine_kernel(const float* __restrict__ y, const int* __restrict__ place,
     const long long n = blockIdx.x;
     for (int c = threadIdx.x; c < width; c += 256) {
         float sum = 0.f;
-        for (int s = 0; s < top; ++s)
-            sum = fmaf(weights[n * top + s], y[(size_t)place[n * top + s] * width + c], sum);
+        for (int s = 0; s < top; ++s) {
+            float v = y[(size_t)place[n * top + s] * width + c];
+            sum = weights ? fmaf(weights[n * top + s], v, sum) : sum + v;
+        }
         residual[(size_t)n * width + c] += sum;
     }
 }
@@ -213,6 +227,9 @@ static int configure_grouped() {
                                  (int)kGroupedSmem);
     if (e == cudaSuccess)
         e = cudaFuncSetAttribute(grouped_mma_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)kGroupedSmem);
+    if (e == cudaSuccess)
+        e = cudaFuncSetAttribute(grouped_mma_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  (int)kGroupedSmem);
     if (e != cudaSuccess) return (int)e;
     configured = true;
@@ -273,6 +290,31 @@ NNIS_API int nnis_moe_grouped(const void* x, const void* w_up, const void* w_dow
     grouped_mma_kernel<1><<<dim3(tiles, (width + 63) / 64), 128, smem, stream>>>(
         (const bf16*)act, ff, perm, top, (const bf16*)w_down, tile_expert, y, width, ff, 0, 0, 0, 0);
     moe_combine_kernel<<<n_tokens, 256, 0, stream>>>(y, place, weights, residual, width, top);
+    NNIS_RETURN_LAUNCH();
+}
+
+// Gated experts with the scores on their inputs: w_gu [experts, 2 ff, width] with the gate's and
+// the up-projection's rows interleaved; the rest as nnis_moe_grouped (act [tiles * 64, ff]).
+NNIS_API int nnis_moe_grouped_gated(const void* x, const void* w_gu, const void* w_down, const int* ids,
+                                    const float* weights, int* perm, int* place, int* tile_expert, void* act,
+                                    float* y, float* residual, int n_tokens, int width, int ff, int experts,
+                                    int top, cudaStream_t stream) {
+    if (n_tokens <= 0 || top <= 0 || !x || !w_gu || !w_down || !ids || !weights || !perm || !place ||
+        !tile_expert || !act || !y || !residual)
+        return NNIS_ERR_ARGUMENT;
+    if (!nnis_moe_grouped_takes(width, ff, experts)) return NNIS_ERR_UNSUPPORTED;
+    if (((uintptr_t)x | (uintptr_t)w_gu | (uintptr_t)w_down | (uintptr_t)act) % 16) return NNIS_ERR_ALIGNMENT;
+    const long long pairs = (long long)n_tokens * top;
+    const int tiles = nnis_moe_grouped_tiles(pairs, experts);
+    moe_sort_kernel<<<1, 1024, (3 * experts + 1) * sizeof(int), stream>>>(ids, (int)pairs, experts, tiles,
+                                                                         kGroupRows, perm, place, tile_expert);
+    int code = configure_grouped();
+    if (code != NNIS_OK) return code;
+    grouped_mma_kernel<3><<<dim3(tiles, (2 * ff + 63) / 64), 128, kGroupedSmem, stream>>>(
+        (const bf16*)x, width, perm, top, (const bf16*)w_gu, tile_expert, act, 2 * ff, width, 0, 0, 0, 0, weights);
+    grouped_mma_kernel<1><<<dim3(tiles, (width + 63) / 64), 128, kGroupedSmem, stream>>>(
+        (const bf16*)act, ff, perm, top, (const bf16*)w_down, tile_expert, y, width, ff, 0, 0, 0, 0);
+    moe_combine_kernel<<<n_tokens, 256, 0, stream>>>(y, place, (const float*)nullptr, residual, width, top);
     NNIS_RETURN_LAUNCH();
 }
 

@@ -1514,7 +1514,7 @@ def moe_experts_gated(h: torch.Tensor, w_gu: torch.Tensor, w_down: torch.Tensor,
                       weights: torch.Tensor, token_pos: torch.Tensor, act: torch.Tensor,
                       residual: torch.Tensor, top: int) -> None:
     """residual[n] += sum over the chosen experts of W_down[e] (silu(W_gate[e] x) * (W_up[e] x)),
-    x = weight * h[n]; w_gu [experts, 2 ff, width] with the gate's rows first."""
+    x = weight * h[n]; w_gu [experts, 2 ff, width], row 2f the gate's and 2f + 1 the up's of feature f."""
     _cuda(h, w_gu, w_down, ids, weights, token_pos, act, residual)
     n, width = h.shape
     experts, ff2, _ = w_gu.shape
@@ -1526,3 +1526,26 @@ def moe_experts_gated(h: torch.Tensor, w_gu: torch.Tensor, w_down: torch.Tensor,
     _check(_lib().nnis_moe_experts_gated(_ptr(h), _ptr(w_gu), _ptr(w_down), _ptr(ids), _ptr(weights),
                                          _ptr(token_pos), _ptr(act), _ptr(residual), n, width, ff, top,
                                          code_of(h.dtype), _stream()), "moe_experts_gated", 2)
+
+
+def moe_grouped_gated(h: torch.Tensor, w_gu: torch.Tensor, w_down: torch.Tensor, ids: torch.Tensor,
+                      weights: torch.Tensor, perm: torch.Tensor, place: torch.Tensor, tile_expert: torch.Tensor,
+                      act: torch.Tensor, y: torch.Tensor, residual: torch.Tensor, top: int) -> None:
+    """``moe_experts_gated`` for many tokens in bfloat16: the pairs sorted by expert in runs padded to 64
+    rows, two grouped products on mma.sync tiles (the first with the gated activation and the score in
+    its epilogue), then the plain sum of each token's experts.  Scratch as ``moe_grouped``."""
+    _cuda(h, w_gu, w_down, ids, weights, perm, place, tile_expert, act, y, residual)
+    n, width = h.shape
+    experts, ff2, _ = w_gu.shape
+    ff = ff2 // 2
+    tiles = moe_grouped_tiles(n * top, experts)
+    _need(h.dtype == w_gu.dtype == w_down.dtype == act.dtype == torch.bfloat16
+          and tuple(w_gu.shape) == (experts, 2 * ff, width) and tuple(w_down.shape) == (experts, width, ff),
+          "moe_grouped_gated: bfloat16 stacked weights")
+    _need(perm.numel() >= tiles * 64 and place.numel() >= n * top and tile_expert.numel() >= tiles
+          and act.numel() >= tiles * 64 * ff and y.dtype == torch.float32 and y.numel() >= tiles * 64 * width,
+          "moe_grouped_gated: scratch too small")
+    _need(residual.dtype == torch.float32 and tuple(residual.shape) == (n, width), "moe_grouped_gated: residual")
+    _check(_lib().nnis_moe_grouped_gated(_ptr(h), _ptr(w_gu), _ptr(w_down), _ptr(ids), _ptr(weights), _ptr(perm),
+                                         _ptr(place), _ptr(tile_expert), _ptr(act), _ptr(y), _ptr(residual), n, width,
+                                         ff, experts, top, _stream()), "moe_grouped_gated", 4)

@@ -19,8 +19,9 @@ mma.sync tiles where it gets few.
 A second form (``activation`` "silu_gated"): the expert is W_down (silu(W_gate x) * (W_up x))
 with x = score * h: the router's scores are sigmoid(z) (``scores`` "sigmoid"), used as they
 are, and they multiply the expert's INPUT (``weight_on`` "input"); the output is the plain sum
-of the chosen experts'.  Gate and up are stacked per expert ([experts, 2 ff, width]); the score
-multiplies their float32 sums, which is the product with score * h.
+of the chosen experts'.  Gate and up are stacked per expert with their rows interleaved ([experts,
+2 ff, width]); the score multiplies their float32 sums, which is the product with score * h.
+Prompt steps in bfloat16 sort the pairs by expert and run grouped products on mma.sync tiles.
 
 params: hidden_size, experts, top, ff, shared_ff (0: no shared expert), activation
 ("relu2" | "silu_gated"), scores ("softmax" over the chosen logits | "sigmoid"), weight_on
@@ -91,9 +92,9 @@ class MoEFeedForward(Part):
         self.w_router = tensors[self.tensor_name(self.names["router"])]
         self.b_router = tensors[self.tensor_name(self.names["router_bias"])] \
             if self.names.get("router_bias") else None
-        if self.gated:  # gate rows, then up rows, per expert
-            self.w_up = torch.stack([torch.cat([tensors[self._expert(e, "gate")], tensors[self._expert(e, "up")]], 0)
-                                     for e in range(self.experts)]).contiguous()
+        if self.gated:  # per expert, row 2f the gate's and row 2f + 1 the up-projection's of feature f
+            self.w_up = torch.stack([torch.stack([tensors[self._expert(e, "gate")], tensors[self._expert(e, "up")]], 1)
+                                     .reshape(2 * self.ff, self.hidden) for e in range(self.experts)]).contiguous()
         else:
             self.w_up = torch.stack([tensors[self._expert(e, "up")] for e in range(self.experts)]).contiguous()
         self.w_down = torch.stack([tensors[self._expert(e, "down")] for e in range(self.experts)]).contiguous()
@@ -134,6 +135,16 @@ class MoEFeedForward(Part):
         weights = ws.get("moe_weights", (n, self.top), torch.float32)
         ops.moe_route(x, self.w_router, self.b_router, ctx.token_pos, ids, weights, self.top,
                       sigmoid_scores=self.scores == "sigmoid")
+        if self.gated and self.dtype == torch.bfloat16 and not ctx.decode and n >= self.GROUPED_FROM \
+                and ops.MOE_GROUPED and ops.moe_grouped_takes(self.hidden, self.ff, self.experts):
+            tiles = ops.moe_grouped_tiles(n * self.top, self.experts)
+            ops.moe_grouped_gated(x, self.w_up, self.w_down, ids, weights,
+                                  ws.get("moe_perm", (tiles * 64,), torch.int32),
+                                  ws.get("moe_place", (n * self.top,), torch.int32),
+                                  ws.get("moe_tile_expert", (tiles,), torch.int32),
+                                  ws.get("moe_act_sorted", (tiles * 64, self.ff), self.dtype),
+                                  ws.get("moe_y_sorted", (tiles * 64, self.hidden), torch.float32), residual, self.top)
+            return
         if self.gated:
             act = ws.get("moe_act", (n, self.top, self.ff), self.dtype)
             ops.moe_experts_gated(x, self.w_up, self.w_down, ids, weights, ctx.token_pos, act, residual, self.top)

@@ -91,7 +91,13 @@ ONLY_MOE = config(150, 72, 1e-5, 0.5, None, [layer(wkv(1, 8, 4), moe(7, 3, 40))]
 SHARP = config(150, 64, 1e-5, 0.5, None, [
     layer(attention(4, 2, 16, 16, 8, 1.5, base=100.0, chunk=192), None),
     layer(attention(4, 2, 16, 16, 8, 1.5, base=100.0, chunk=70, kv_from=0), None)])
-CONFIGS: Dict[str, dict] = {"mixed": MIXED, "odd": ODD, "attention": ONLY_ATTENTION, "wkv": ONLY_WKV,
+# key and value heads of 64 and of 128: the sizes of the tensor-core prompt attention; a layer that
+# reads another's keys under a smaller chunk, a chunk that is no multiple of a page, one without a cap
+HEADS_64 = config(150, 64, 1e-5, 0.6, None, [
+    layer(attention(4, 2, 64, 64, 32, 0.2, base=100.0, softcap=12.0, chunk=100), None),
+    layer(attention(6, 2, 64, 64, 32, 0.4, base=100.0, chunk=37, kv_from=0), dense(40, 2.0)),
+    layer(attention(2, 1, 128, 128, 128, 0.15, base=5000.0, scaling=(4.0, 1.0, 2.0, 128), softcap=30.0), None)])
+CONFIGS: Dict[str, dict] = {"mixed": MIXED, "heads64": HEADS_64, "odd": ODD, "attention": ONLY_ATTENTION, "wkv": ONLY_WKV,
                             "wide_wkv": WIDE_WKV, "mamba": ONLY_MAMBA, "wide_mamba": WIDE_MAMBA,
                             "dense": ONLY_DENSE, "moe": ONLY_MOE, "sharp": SHARP}
 

@@ -160,7 +160,7 @@ def test_scaled_frequencies_follow_the_three_ranges():
 
 # ---- whole models ------------------------------------------------------------------------------
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("name", ["attention", "wkv", "wide_wkv", "mamba", "wide_mamba", "dense", "moe"])
+@pytest.mark.parametrize("name", ["attention", "heads64", "wkv", "wide_wkv", "mamba", "wide_mamba", "dense", "moe"])
 def test_each_mechanism_alone(models, name, dtype, tmp_path):
     rng = random.Random(11)
     vocab = read_config(models[name])["vocab"]
@@ -177,7 +177,7 @@ def test_each_mechanism_alone(models, name, dtype, tmp_path):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("name", ["mixed", "odd"])
+@pytest.mark.parametrize("name", ["mixed", "odd", "heads64"])
 def test_whole_last_tokens_and_unequal_batches(models, name, dtype, tmp_path):
     vocab = read_config(models[name])["vocab"]
     trace, sequences = three_cuts(random.Random(3), vocab)
