@@ -1344,9 +1344,13 @@ def wkv_mix(x: torch.Tensor, mu: torch.Tensor, prev: torch.Tensor, token_pos: to
 def wkv_scan(r: torch.Tensor, k: torch.Tensor, v: torch.Tensor, d: torch.Tensor, u: torch.Tensor,
              state: torch.Tensor, token_pos: torch.Tensor, token_seq: torch.Tensor, seq_slots: torch.Tensor,
              seq_first_row: Optional[torch.Tensor], seq_count: Optional[torch.Tensor], o_raw: torch.Tensor,
-             heads: int, dim: int) -> None:
-    """The recurrence over the step's tokens, from and into ``state`` [slots, heads, dim, dim]."""
-    _cuda(r, k, v, d, u, state, o_raw)
+             heads: int, dim: int, segments: Optional[torch.Tensor] = None,
+             seq_first_segment: Optional[torch.Tensor] = None, seg_len: int = 0,
+             seg_state: Optional[torch.Tensor] = None, seg_logw: Optional[torch.Tensor] = None) -> None:
+    """The recurrence over the step's tokens, from and into ``state`` [slots, heads, dim, dim].  With
+    ``segments`` (``scan_segments``) a prompt step's sequences are cut into runs of ``seg_len`` tokens that
+    are worked side by side; scratch ``seg_state`` float32 [runs, heads, dim, dim], ``seg_logw`` [runs, heads, dim]."""
+    _cuda(r, k, v, d, u, state, o_raw, segments, seq_first_segment, seg_state, seg_logw)
     _seq_tables(token_pos, token_seq, seq_slots, seq_first_row, seq_count)
     n = r.shape[0]
     _need(r.dtype == k.dtype == v.dtype and tuple(r.shape) == tuple(k.shape) == tuple(v.shape) == (n, heads * dim),
@@ -1356,9 +1360,20 @@ def wkv_scan(r: torch.Tensor, k: torch.Tensor, v: torch.Tensor, d: torch.Tensor,
           and tuple(state.shape[1:]) == (heads, dim, dim), "wkv_scan: float32 decay rows, bonus, state, output")
     _need(dim <= 256, f"wkv_scan: heads of {dim} channels (at most 256)")
     units = seq_first_row.numel() if seq_first_row is not None else n
+    n_segments = 0
+    if segments is not None:
+        n_segments = segments.shape[0]
+        _need(seq_first_row is not None and seq_first_segment is not None and seg_len > 0
+              and seg_state is not None and seg_state.dtype == torch.float32
+              and seg_state.numel() >= n_segments * heads * dim * dim and seg_logw is not None
+              and seg_logw.dtype == torch.float32 and seg_logw.numel() >= n_segments * heads * dim
+              and segments.dtype == seq_first_segment.dtype == torch.int32,
+              "wkv_scan: runs need a prompt step, their tables and scratch")
     _check(_lib().nnis_wkv_scan(_ptr(r), _ptr(k), _ptr(v), _ptr(d), _ptr(u), _ptr(state), _ptr(token_pos),
                                 _ptr(token_seq), _ptr(seq_slots), _ptr(seq_first_row), _ptr(seq_count),
-                                _ptr(o_raw), units, heads, dim, code_of(r.dtype), _stream()), "wkv_scan")
+                                _ptr(segments), n_segments, _ptr(seq_first_segment), seg_len, _ptr(seg_state),
+                                _ptr(seg_logw), _ptr(o_raw), units, heads, dim, code_of(r.dtype), _stream()),
+           "wkv_scan", 3 if segments is not None else 1)
 
 
 def wkv_finish(o_raw: torch.Tensor, gate: torch.Tensor, norm_w: torch.Tensor, x: torch.Tensor,
@@ -1401,10 +1416,14 @@ def selective_scan(xc: torch.Tensor, xz: torch.Tensor, dt_raw: torch.Tensor, bc:
                    a_log: torch.Tensor, dskip: torch.Tensor, state: torch.Tensor, conv_state: torch.Tensor,
                    token_pos: torch.Tensor, token_seq: torch.Tensor, seq_slots: torch.Tensor,
                    seq_first_row: Optional[torch.Tensor], seq_count: Optional[torch.Tensor], y: torch.Tensor,
-                   taps: int) -> None:
+                   taps: int, segments: Optional[torch.Tensor] = None,
+                   seq_first_segment: Optional[torch.Tensor] = None, seg_len: int = 0,
+                   seg_state: Optional[torch.Tensor] = None, seg_dt: Optional[torch.Tensor] = None) -> None:
     """y = (scan over the step's tokens + D * xc) * silu(z), from and into ``state`` [slots, inner, N];
-    moves ``conv_state`` on by the step's inputs."""
-    _cuda(xc, xz, dt_raw, bc, a_log, dskip, state, conv_state, y)
+    moves ``conv_state`` on by the step's inputs.  With ``segments`` (``scan_segments``) a prompt step's
+    sequences are cut into runs of ``seg_len`` tokens that are worked side by side; scratch ``seg_state``
+    float32 [runs, inner, N] and ``seg_dt`` float32 [runs, inner]."""
+    _cuda(xc, xz, dt_raw, bc, a_log, dskip, state, conv_state, y, segments, seq_first_segment, seg_state, seg_dt)
     _seq_tables(token_pos, token_seq, seq_slots, seq_first_row, seq_count)
     n, inner = xc.shape
     N = a_log.shape[1]
@@ -1414,12 +1433,32 @@ def selective_scan(xc: torch.Tensor, xz: torch.Tensor, dt_raw: torch.Tensor, bc:
           and tuple(dt_raw.shape) == (n, inner) and tuple(bc.shape) == (n, 2 * N) and a_log.shape[0] == inner
           and dskip.numel() == inner and tuple(state.shape[1:]) == (inner, N),
           "selective_scan: float32 dt [n, inner], bc [n, 2 N], A_log [inner, N], D [inner], state")
-    _need(N <= 384, f"selective_scan: {N} state values a channel (at most 384)")
+    _need(N <= 256, f"selective_scan: {N} state values a channel (at most 256)")
     units = seq_first_row.numel() if seq_first_row is not None else n
+    n_segments = 0
+    if segments is not None:
+        n_segments = segments.shape[0]
+        _need(seq_first_row is not None and seq_first_segment is not None and seg_len > 0
+              and seg_state is not None and seg_state.dtype == torch.float32
+              and seg_state.numel() >= n_segments * inner * N and seg_dt is not None
+              and seg_dt.dtype == torch.float32 and seg_dt.numel() >= n_segments * inner
+              and segments.dtype == seq_first_segment.dtype == torch.int32,
+              "selective_scan: runs need a prompt step, their tables and scratch")
     _check(_lib().nnis_selective_scan(_ptr(xc), _ptr(xz), _ptr(dt_raw), _ptr(bc), _ptr(a_log), _ptr(dskip),
                                       _ptr(state), _ptr(conv_state), _ptr(token_pos), _ptr(token_seq),
-                                      _ptr(seq_slots), _ptr(seq_first_row), _ptr(seq_count), _ptr(y), units, inner,
-                                      N, taps, code_of(xc.dtype), _stream()), "selective_scan")
+                                      _ptr(seq_slots), _ptr(seq_first_row), _ptr(seq_count), _ptr(segments),
+                                      n_segments, _ptr(seq_first_segment), seg_len, _ptr(seg_state), _ptr(seg_dt),
+                                      _ptr(y), units, inner, N, taps, code_of(xc.dtype), _stream()),
+           "selective_scan", 3 if segments is not None else 1)
+
+
+SCAN_SEGMENT = int(os.environ.get("NNIS_SCAN_SEGMENT", "64"))  # tokens of a run of the recurrent mixers; 0: no runs
+
+
+def scan_segments(counts, seg_len: int):
+    """(segments [n, 2] = (sequence, first token of the run), first run of every sequence
+    [sequences + 1]) for a prompt step whose sequences bring ``counts`` tokens."""
+    return retention_segments(counts, seg_len)
 
 
 def qkv_prep(a: torch.Tensor, wq: Optional[torch.Tensor], wk: Optional[torch.Tensor],

@@ -13,7 +13,8 @@
 //   wkv_scan     a CTA per (sequence, head) walks the step's tokens in order, 16 (or fewer)
 //                at a time through shared memory; a thread holds a run of key channels of
 //                one value column of S in registers; partial outputs of the runs are added
-//                up per tile of tokens
+//                up per tile of tokens.  Long prompts: runs of tokens side by side in two
+//                passes with wkv_prefix between them (see the kernel)
 //   wkv_finish   o / rms(o) per head, times the norm's weights, times silu(gate), rounded
 //                once; the step's last row of every sequence becomes the state's h'
 //
@@ -69,14 +70,25 @@ wkv_mix_kernel(const T* __restrict__ x, const float* __restrict__ mu, const floa
 }
 
 // KL: key channels a thread holds.  Threads: dim value columns x KS runs of KL key channels.
-template <typename T, int KL>
+//
+// PASS 0: a unit is a sequence of the step (or a row, in steps of single tokens): from the slot's
+//         state to the slot's state, outputs written.
+// Long prompts are cut into runs of `seg_len` tokens that are worked side by side (the recurrence is
+// linear in the state): a unit is then a run, (sequence, first token) in `segments`, and
+// PASS 1: from a zero state; what the run adds to the state goes to seg_state[run, head], the sum of
+//         the logarithms of its decays per key channel to seg_logw[run, head] (the state before the
+//         run decays by exp of that sum over it); wkv_prefix_kernel then turns seg_state[run] into
+//         the state BEFORE each run and leaves the slot's state as it is after the step;
+// PASS 2: from seg_state[run], outputs written.
+template <typename T, int KL, int PASS>
 __global__ void __launch_bounds__(1024)
 wkv_scan_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __restrict__ v,
                 const float* __restrict__ d, const float* __restrict__ u, float* __restrict__ state,
                 const int* __restrict__ token_pos, const int* __restrict__ token_seq,
                 const int* __restrict__ seq_slots, const int* __restrict__ seq_first_row,
-                const int* __restrict__ seq_count, float* __restrict__ o_raw, int heads, int dim, int KS,
-                int TT) {
+                const int* __restrict__ seq_count, const int* __restrict__ segments, int seg_len,
+                float* __restrict__ seg_state, float* __restrict__ seg_logw, float* __restrict__ o_raw,
+                int heads, int dim, int KS, int TT) {
     extern __shared__ float smem[];
     pdl_wait();
     pdl_launch_dependents();
@@ -86,10 +98,15 @@ wkv_scan_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __res
     float* ws = ks + TT * dimP;       // [TT][dimP]
     float* vs = ws + TT * dimP;       // [TT][dim]
     float* us = vs + TT * dim;        // [dimP]
-    float* part = us + dimP;          // [TT][KS][dim]
+    float* part = us + dimP;          // [TT][KS][dim]; PASS 1: [TT][dimP] logarithms of the decays
     const int unit = blockIdx.x, h = blockIdx.y;
     int first, count, slot;
-    if (seq_first_row) {
+    if (PASS != 0) {
+        const int seq = segments[2 * unit], t0 = segments[2 * unit + 1];
+        first = seq_first_row[seq] + t0;
+        count = min(seg_len, seq_count[seq] - t0);
+        slot = seq_slots[seq];
+    } else if (seq_first_row) {
         first = seq_first_row[unit];
         count = seq_count[unit];
         slot = seq_slots[unit];
@@ -102,11 +119,13 @@ wkv_scan_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __res
     const int threads = dim * KS;
     const int j = threadIdx.x % dim, run = threadIdx.x / dim, k0 = run * KL;
     const size_t row_len = (size_t)heads * dim;
-    float* S = state + ((size_t)slot * heads + h) * dim * dim;
+    float* S = PASS == 0 ? state + ((size_t)slot * heads + h) * dim * dim
+                         : seg_state + ((size_t)unit * heads + h) * dim * dim;
     float s[KL];
 #pragma unroll
-    for (int kk = 0; kk < KL; ++kk) s[kk] = (k0 + kk < dim) ? S[(size_t)(k0 + kk) * dim + j] : 0.f;
+    for (int kk = 0; kk < KL; ++kk) s[kk] = (PASS != 1 && k0 + kk < dim) ? S[(size_t)(k0 + kk) * dim + j] : 0.f;
     for (int i = threadIdx.x; i < dimP; i += threads) us[i] = i < dim ? u[(size_t)h * dim + i] : 0.f;
+    float logw = 0.f;  // PASS 1: thread i < dim adds up the logarithms of key channel i's decays
     for (int t0 = 0; t0 < count; t0 += TT) {
         const int tn = min(TT, count - t0);
         __syncthreads();  // the tile before has been added up and written
@@ -114,9 +133,11 @@ wkv_scan_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __res
             int t = i / dimP, c = i - t * dimP;
             size_t at = (size_t)(first + t0 + t) * row_len + (size_t)h * dim + c;
             bool in = c < dim;
-            rs[i] = in ? to_float(r[at]) : 0.f;
+            float lw = in ? -expf(d[at]) : 0.f;
+            if (PASS != 1) rs[i] = in ? to_float(r[at]) : 0.f;
             ks[i] = in ? to_float(k[at]) : 0.f;
-            ws[i] = in ? expf(-expf(d[at])) : 0.f;
+            ws[i] = in ? expf(lw) : 0.f;
+            if (PASS == 1) part[i] = lw;
             if (in) vs[t * dim + c] = to_float(v[at]);
         }
         __syncthreads();
@@ -129,10 +150,15 @@ wkv_scan_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __res
 #pragma unroll
             for (int kk = 0; kk < KL; ++kk) {
                 float kv = kt[kk] * vj;
-                o = fmaf(rt[kk], fmaf(us[k0 + kk], kv, s[kk]), o);
+                if (PASS != 1) o = fmaf(rt[kk], fmaf(us[k0 + kk], kv, s[kk]), o);
                 s[kk] = fmaf(wt[kk], s[kk], kv);
             }
-            part[(t * KS + run) * dim + j] = o;
+            if (PASS != 1) part[(t * KS + run) * dim + j] = o;
+        }
+        if (PASS == 1) {
+            if (threadIdx.x < dim)
+                for (int t = 0; t < tn; ++t) logw += part[t * dimP + threadIdx.x];
+            continue;
         }
         __syncthreads();
         for (int i = threadIdx.x; i < tn * dim; i += threads) {
@@ -142,9 +168,37 @@ wkv_scan_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __res
             o_raw[(size_t)(first + t0 + t) * row_len + (size_t)h * dim + c] = o;
         }
     }
+    if (PASS != 2) {
 #pragma unroll
-    for (int kk = 0; kk < KL; ++kk)
-        if (k0 + kk < dim) S[(size_t)(k0 + kk) * dim + j] = s[kk];
+        for (int kk = 0; kk < KL; ++kk)
+            if (k0 + kk < dim) S[(size_t)(k0 + kk) * dim + j] = s[kk];
+    }
+    if (PASS == 1 && threadIdx.x < dim) seg_logw[((size_t)unit * heads + h) * dim + threadIdx.x] = logw;
+}
+
+// Between the two passes over the runs: a thread per (sequence, head, key channel, value channel)
+// walks the sequence's runs in order.  seg_state[run] (what the run added) becomes the state before
+// the run; the slot's state becomes the state after the last run.
+__global__ void __launch_bounds__(256)
+wkv_prefix_kernel(float* __restrict__ state, const int* __restrict__ seq_slots,
+                  const int* __restrict__ seq_first_segment, float* __restrict__ seg_state,
+                  const float* __restrict__ seg_logw, int heads, int dim) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const int seq = blockIdx.x;
+    const size_t per_seq = (size_t)heads * dim * dim;
+    const size_t idx = (size_t)blockIdx.y * 256 + threadIdx.x;
+    if (idx >= per_seq) return;
+    const size_t hk = idx / dim;  // head * dim + key channel
+    float* S = state + (size_t)seq_slots[seq] * per_seq + idx;
+    float carry = *S;
+    for (int run = seq_first_segment[seq]; run < seq_first_segment[seq + 1]; ++run) {
+        float* at = seg_state + (size_t)run * per_seq + idx;
+        float added = *at;
+        *at = carry;
+        carry = fmaf(expf(seg_logw[(size_t)run * heads * dim + hk]), carry, added);
+    }
+    *S = carry;
 }
 
 // a CTA per row; a warp per head in turn
@@ -192,20 +246,41 @@ static int wkv_launch(const void* x, const float* mu, float* prev, const int* to
     return e == cudaSuccess ? NNIS_OK : (int)e;
 }
 
-template <typename T, int KL>
+template <typename T, int KL, int PASS>
 static cudaError_t scan_launch(dim3 grid, int threads, size_t smem, cudaStream_t stream, const void* r,
                                const void* k, const void* v, const float* d, const float* u, float* state,
                                const int* token_pos, const int* token_seq, const int* seq_slots,
-                               const int* seq_first_row, const int* seq_count, float* o_raw, int heads, int dim,
-                               int KS, int TT) {
+                               const int* seq_first_row, const int* seq_count, const int* segments, int seg_len,
+                               float* seg_state, float* seg_logw, float* o_raw, int heads, int dim, int KS, int TT) {
     if (smem > 48 * 1024) {
-        cudaError_t e = cudaFuncSetAttribute(wkv_scan_kernel<T, KL>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             (int)smem);
+        cudaError_t e = cudaFuncSetAttribute(wkv_scan_kernel<T, KL, PASS>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return e;
     }
-    return launch_dependent(wkv_scan_kernel<T, KL>, grid, threads, smem, stream, (const T*)r, (const T*)k,
+    return launch_dependent(wkv_scan_kernel<T, KL, PASS>, grid, threads, smem, stream, (const T*)r, (const T*)k,
                             (const T*)v, d, u, state, token_pos, token_seq, seq_slots, seq_first_row, seq_count,
-                            o_raw, heads, dim, KS, TT);
+                            segments, seg_len, seg_state, seg_logw, o_raw, heads, dim, KS, TT);
+}
+
+template <typename T, int KL>
+static cudaError_t scan_passes(int units, int n_segments, int threads, size_t smem, cudaStream_t stream,
+                               const void* r, const void* k, const void* v, const float* d, const float* u,
+                               float* state, const int* token_pos, const int* token_seq, const int* seq_slots,
+                               const int* seq_first_row, const int* seq_count, const int* segments,
+                               const int* seq_first_segment, int seg_len, float* seg_state, float* seg_logw,
+                               float* o_raw, int heads, int dim, int KS, int TT) {
+#define NNIS_WKV_ARGS r, k, v, d, u, state, token_pos, token_seq, seq_slots, seq_first_row, seq_count, segments, \
+                      seg_len, seg_state, seg_logw, o_raw, heads, dim, KS, TT
+    if (!segments)
+        return scan_launch<T, KL, 0>(dim3(units, heads), threads, smem, stream, NNIS_WKV_ARGS);
+    cudaError_t e = scan_launch<T, KL, 1>(dim3(n_segments, heads), threads, smem, stream, NNIS_WKV_ARGS);
+    if (e != cudaSuccess) return e;
+    const size_t per_seq = (size_t)heads * dim * dim;
+    e = launch_dependent(wkv_prefix_kernel, dim3(units, (unsigned)((per_seq + 255) / 256)), 256, 0, stream, state,
+                         seq_slots, seq_first_segment, seg_state, (const float*)seg_logw, heads, dim);
+    if (e != cudaSuccess) return e;
+    return scan_launch<T, KL, 2>(dim3(n_segments, heads), threads, smem, stream, NNIS_WKV_ARGS);
+#undef NNIS_WKV_ARGS
 }
 
 }  // namespace nnis
@@ -229,11 +304,18 @@ NNIS_API int nnis_wkv_mix(const void* x, const float* mu, float* prev, const int
 // r, k, v: operand dtype [n, heads * dim]; d: float32 [n, heads * dim] (the decay's projection,
 // w = exp(-exp(d))); u: float32 [heads, dim]; state: float32 [slots, heads, dim, dim];
 // o_raw: float32 [n, heads * dim].  `units`: sequences of the step (with seq_first_row) or rows.
+// With `segments` (int32 [n_segments, 2] = (sequence, first token of the run), runs of seg_len
+// tokens), seq_first_segment [sequences + 1] and scratch seg_state float32 [n_segments, heads, dim,
+// dim] and seg_logw float32 [n_segments, heads, dim] the runs are worked side by side.
 NNIS_API int nnis_wkv_scan(const void* r, const void* k, const void* v, const float* d, const float* u,
                            float* state, const int* token_pos, const int* token_seq, const int* seq_slots,
-                           const int* seq_first_row, const int* seq_count, float* o_raw, int units, int heads,
-                           int dim, int dtype, cudaStream_t stream) {
+                           const int* seq_first_row, const int* seq_count, const int* segments, int n_segments,
+                           const int* seq_first_segment, int seg_len, float* seg_state, float* seg_logw,
+                           float* o_raw, int units, int heads, int dim, int dtype, cudaStream_t stream) {
     if (units <= 0 || heads <= 0 || dim <= 0 || !r || !k || !v || !d || !u || !state || !o_raw)
+        return NNIS_ERR_ARGUMENT;
+    if (segments && (!seq_first_row || !seq_first_segment || !seg_state || !seg_logw || seg_len <= 0 ||
+                     n_segments <= 0))
         return NNIS_ERR_ARGUMENT;
     if (dim > 256 || heads > 65535) return NNIS_ERR_UNSUPPORTED;
     // as many runs of key channels as keep the CTA at 256 threads or more, at most 1,024
@@ -243,14 +325,16 @@ NNIS_API int nnis_wkv_scan(const void* r, const void* k, const void* v, const fl
     if (threads > 1024) return NNIS_ERR_UNSUPPORTED;
     int dimP = KS * KL;
     int TT = seq_first_row ? 16 : 1;
-    auto bytes = [&](int tt) { return sizeof(float) * ((size_t)tt * (3 * dimP + dim + KS * dim) + dimP); };
+    auto bytes = [&](int tt) {
+        return sizeof(float) * ((size_t)tt * (3 * dimP + dim + (size_t)max(KS * dim, dimP)) + dimP);
+    };
     while (TT > 1 && bytes(TT) > 96 * 1024) TT >>= 1;
     size_t smem = bytes(TT);
-    dim3 grid(units, heads);
     cudaError_t e;
 #define NNIS_WKV_CASE(T, KLV) \
-    e = scan_launch<T, KLV>(grid, threads, smem, stream, r, k, v, d, u, state, token_pos, token_seq, seq_slots, \
-                            seq_first_row, seq_count, o_raw, heads, dim, KS, TT)
+    e = scan_passes<T, KLV>(units, n_segments, threads, smem, stream, r, k, v, d, u, state, token_pos, token_seq, \
+                            seq_slots, seq_first_row, seq_count, segments, seq_first_segment, seg_len, seg_state, \
+                            seg_logw, o_raw, heads, dim, KS, TT)
     if (dtype == NNIS_DTYPE_F32) {
         if (KL == 8) NNIS_WKV_CASE(float, 8);
         else if (KL == 16) NNIS_WKV_CASE(float, 16);

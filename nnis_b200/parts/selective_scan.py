@@ -12,7 +12,10 @@ The output y * silu(z) goes through W_o into the residual rows the part is given
 the convolution's last taps - 1 inputs are float32 in the cache's state area, one of each per
 slot, zero when a slot is taken, so a later portion of a prompt or a single token goes on
 from what the tokens before left.  Step sizes, decays, B and C, the state and the sums are
-float32 in every dtype.
+float32 in every dtype.  A long prompt is cut into runs of tokens that start from zero side by
+side; the states between the runs are then put together in order (the recurrence is linear in
+the state, and a run's decay is exp(A * the sum of its step sizes)), and a second pass over the
+runs, each from its true state, writes the outputs.
 
 params: hidden_size, inner, state, dt_rank, taps, names {in, conv, conv_bias, x, dt,
 dt_bias, a_log, d, o}.
@@ -39,8 +42,8 @@ class SelectiveScan(Part):
         self.rank = int(params["dt_rank"])
         self.taps = int(params["taps"])
         self.names = params["names"]
-        if not 0 < self.state <= 384:
-            raise ValueError(f"selective scan kernels take up to 384 state values a channel; got {self.state}")
+        if not 0 < self.state <= 256:
+            raise ValueError(f"selective scan kernels take up to 256 state values a channel; got {self.state}")
         if self.taps < 1:
             raise ValueError("selective scan: the convolution has at least one tap")
         self.w_in = self.w_dt_low = self.w_bc = self.w_dt = self.w_o = None
@@ -90,6 +93,17 @@ class SelectiveScan(Part):
         W, I, N, R = self.hidden, self.inner, self.state, self.rank
         return 2.0 * sum(counts) * (3 * W * I + I * (R + 2 * N) + I * R + I * self.taps + 3 * I * N)
 
+    SEGMENTS, FIRST_SEGMENT = "scan/segments", "scan/first_segment"
+
+    def step_tables(self, counts, starts, have=()):
+        """Prompt steps with a sequence longer than two runs: the runs of every sequence, worked side
+        by side (the same list for every recurrent layer of the model that cuts its prompts so)."""
+        seg = ops.SCAN_SEGMENT
+        if seg <= 0 or max(counts) <= 2 * seg or self.SEGMENTS in have:
+            return {}
+        segments, first = ops.scan_segments(counts, seg)
+        return {self.SEGMENTS: segments, self.FIRST_SEGMENT: first}
+
     def forward(self, x: torch.Tensor, ctx, residual: torch.Tensor, cache: StateView) -> None:
         n = residual.shape[0]
         I, N, ws = self.inner, self.state, ctx.workspace
@@ -106,8 +120,14 @@ class SelectiveScan(Part):
         dt_raw = ws.get("scan_dt", (n, I), torch.float32)
         linear(dt_low, self.w_dt, self.dt_bias, dt_raw, STORE_F32, decode=ctx.decode)
         y = ws.get("scan_y", (n, I), self.dtype)
+        segments = ctx.tables.get(self.SEGMENTS) if not ctx.decode else None
+        runs = segments.shape[0] if segments is not None else 0
         ops.selective_scan(xc, xz, dt_raw, bc, self.a_log, self.d, state, conv_state, ctx.token_pos,
-                           ctx.token_seq, ctx.seq_slots, ctx.seq_first_row, ctx.seq_count, y, self.taps)
+                           ctx.token_seq, ctx.seq_slots, ctx.seq_first_row, ctx.seq_count, y, self.taps,
+                           segments=segments, seq_first_segment=ctx.tables.get(self.FIRST_SEGMENT),
+                           seg_len=ops.SCAN_SEGMENT,
+                           seg_state=ws.get("scan_run_state", (runs, I, N), torch.float32) if runs else None,
+                           seg_dt=ws.get("scan_run_dt", (runs, I), torch.float32) if runs else None)
         linear(y, self.w_o, None, residual, ADD_F32, ws, decode=ctx.decode)
 
 

@@ -15,7 +15,11 @@ Each head's o is divided by its root mean square, the heads are joined, multipli
 weight per channel and by the gate, and W_o adds the result into the residual rows it is
 given.  S and h' are float32 in the cache's state area, one of each per slot, so a later
 portion of a prompt or a single token goes on from what the tokens before left; the decay,
-the recurrence, the unit norm and the gate's silu are float32 in every dtype.
+the recurrence, the unit norm and the gate's silu are float32 in every dtype.  A long prompt is cut
+into runs of tokens that start from zero side by side; the states between the runs are then put
+together in order (the recurrence is linear in the state, and a run's decay of key channel k is the
+product of its tokens' w_k), and a second pass over the runs, each from its true state, writes the
+outputs.
 
 params: hidden_size, heads, dim, decay_rank, eps, names {mu (a stem; ".r", ".k", ".v",
 ".g", ".w" follow), r, k, v, g, w1, w2, w0, u, norm, o}.
@@ -88,6 +92,17 @@ class WKV(Part):
         W, C = self.hidden, self.heads * self.dim
         return 2.0 * sum(counts) * (5 * W * C + max(self.rank, 0) * (W + C) + 2 * C * self.dim)
 
+    SEGMENTS, FIRST_SEGMENT = "scan/segments", "scan/first_segment"
+
+    def step_tables(self, counts, starts, have=()):
+        """Prompt steps with a sequence longer than two runs: the runs of every sequence, worked side
+        by side (the same list for every recurrent layer of the model that cuts its prompts so)."""
+        seg = ops.SCAN_SEGMENT
+        if seg <= 0 or max(counts) <= 2 * seg or self.SEGMENTS in have:
+            return {}
+        segments, first = ops.scan_segments(counts, seg)
+        return {self.SEGMENTS: segments, self.FIRST_SEGMENT: first}
+
     def forward(self, x: torch.Tensor, ctx, residual: torch.Tensor, cache: StateView) -> None:
         n = residual.shape[0]
         C, ws = self.heads * self.dim, ctx.workspace
@@ -105,7 +120,14 @@ class WKV(Part):
         decay = ws.get("wkv_decay", (n, C), torch.float32)
         linear(low, self.w["w2"], self.w0, decay, STORE_F32, decode=ctx.decode)
         o_raw = ws.get("wkv_o", (n, C), torch.float32)
-        ops.wkv_scan(rkvg[0], rkvg[1], rkvg[2], decay, self.u, state, *seq, o_raw, self.heads, self.dim)
+        segments = ctx.tables.get(self.SEGMENTS) if not ctx.decode else None
+        runs = segments.shape[0] if segments is not None else 0
+        ops.wkv_scan(rkvg[0], rkvg[1], rkvg[2], decay, self.u, state, *seq, o_raw, self.heads, self.dim,
+                     segments=segments, seq_first_segment=ctx.tables.get(self.FIRST_SEGMENT),
+                     seg_len=ops.SCAN_SEGMENT,
+                     seg_state=ws.get("wkv_run_state", (runs, self.heads, self.dim, self.dim), torch.float32)
+                     if runs else None,
+                     seg_logw=ws.get("wkv_run_logw", (runs, self.heads, self.dim), torch.float32) if runs else None)
         out = ws.get("wkv_out", (n, C), self.dtype)
         ops.wkv_finish(o_raw, rkvg[3], self.norm, x, prev, *seq, out, self.heads, self.dim, self.eps)
         linear(out, self.w["o"], None, residual, ADD_F32, ws, decode=ctx.decode)

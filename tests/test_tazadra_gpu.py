@@ -266,6 +266,27 @@ def test_long_decoding_over_page_and_chunk_borders(models, dtype, tmp_path):
     replay_and_check(models, "mixed", dtype, trace, {"a": toks}, tmp_path, "long decoding")
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["wkv", "wide_wkv", "mamba", "wide_mamba", "mixed"])
+def test_long_prompts_of_the_recurrent_mixers_in_runs_and_portions(models, name, dtype, tmp_path):
+    """Prompts longer than two runs of the scans (runs are worked side by side and put together
+    afterwards), alone, in a batch with short ones, continued after a first portion, and decoded on: a
+    state lost or joined wrongly at a run's edge shows, since the slowest channels forget next to
+    nothing over hundreds of tokens."""
+    vocab = read_config(models[name])["vocab"]
+    rng = random.Random(31)
+    a, b, c = (random_tokens(rng, n, vocab) for n in (700, 257, 40))
+    trace = TraceBuilder()
+    trace.step([("a", a[:690], [0, 63, 64, 65, 127, 128, 129, 511, 512, 689])])
+    for t in range(690, 700):
+        trace.step([("a", a[t:t + 1], [0])], end=["a"] if t == 699 else [])
+    trace.step([("b", b[:100], [99]), ("c", c[:39], [38])])          # a first portion, then runs after it
+    trace.step([("b", b[100:], list(range(150, 157))), ("c", c[39:], [0])], end=["b", "c"])
+    trace.step([("a2", a, [256, 600, 699]), ("c2", c, [39]), ("b2", b, [255, 256])], end=["a2", "c2", "b2"])
+    replay_and_check(models, name, dtype, trace, {"a": a, "b": b, "c": c, "a2": a, "c2": c, "b2": b}, tmp_path,
+                     "runs")
+
+
 def test_far_keys_page_borders_chunk_edges_and_the_sink_with_sharp_attention(models, tmp_path):
     """Scores times a large scale and no cap: most of a query's weight lies on one key, and
     the plain implementation says which.  Among those keys are far ones, ones on both sides
