@@ -197,6 +197,24 @@ moe_gather_kernel(const bf16* __restrict__ x, const int* __restrict__ perm, int 
     for (int c = threadIdx.x; c < width / 8; c += 256) dst[c] = p < 0 ? make_uint4(0, 0, 0, 0) : src[c];
 }
 
+// act[row, f] = silu(s g) * (s u) with (g, u) = up[row, 2f], up[row, 2f + 1] (float32 sums of the
+// interleaved gate and up rows) and s the score of the pair that sits at the sorted row
+__global__ void __launch_bounds__(256)
+moe_gated_act_kernel(const float* __restrict__ up, const int* __restrict__ perm, const float* __restrict__ weights,
+                     bf16* __restrict__ act, int ff) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const long long row = blockIdx.x;
+    const int p = perm[row];
+    const float s = p < 0 ? 0.f : weights[p];
+    const float2* in = reinterpret_cast<const float2*>(up + (size_t)row * 2 * ff);
+    for (int f = threadIdx.x; f < ff; f += 256) {
+        float2 gu = in[f];
+        float g = gu.x * s, u = gu.y * s;
+        act[(size_t)row * ff + f] = __float2bfloat16_rn(p < 0 ? 0.f : g / (1.0f + __expf(-g)) * u);
+    }
+}
+
 __global__ void __launch_bounds__(256)
 moe_combine_kernel(const float* __restrict__ y, const int* __restrict__ place,
                    const float* __restrict__ weights, float* __restrict__ residual, int width, int top) {
@@ -354,5 +372,39 @@ NNIS_API int nnis_moe_grouped_tc(const void* x, const void* w_up, const void* w_
                                 stream);
     if (code != NNIS_OK) return code;
     moe_combine_kernel<<<n_tokens, 256, 0, stream>>>(y, place, weights, residual, width, top);
+    NNIS_RETURN_LAUNCH();
+}
+
+// Gated experts with the scores on their inputs, both products on the tcgen05 kernel: the first
+// stores the float32 sums of the interleaved gate and up rows (`up` float32 [tiles * 128, 2 ff]),
+// moe_gated_act applies score and activation, the second product and the unweighted sum follow.
+NNIS_API int nnis_moe_grouped_gated_tc(const void* x, const void* w_gu, const void* w_down, const int* ids,
+                                       const float* weights, int* perm, int* place, int* tile_expert,
+                                       void* x_sorted, float* up, void* act, float* y, float* residual,
+                                       int n_tokens, int width, int ff, int experts, int top, int sm_count,
+                                       int* status, int pdl, cudaStream_t stream) {
+    if (n_tokens <= 0 || top <= 0 || !x || !w_gu || !w_down || !ids || !weights || !perm || !place ||
+        !tile_expert || !x_sorted || !up || !act || !y || !residual)
+        return NNIS_ERR_ARGUMENT;
+    if (!nnis_moe_grouped_takes(width, ff, experts)) return NNIS_ERR_UNSUPPORTED;
+    if (((uintptr_t)x | (uintptr_t)x_sorted | (uintptr_t)up) % 16) return NNIS_ERR_ALIGNMENT;
+    const long long pairs = (long long)n_tokens * top;
+    const int tiles = nnis_moe_grouped_tiles_tc(pairs, experts);
+    const int rows = tiles * 128;
+    moe_sort_kernel<<<1, 1024, (3 * experts + 1) * sizeof(int), stream>>>(ids, (int)pairs, experts, tiles, 128, perm,
+                                                                         place, tile_expert);
+    cudaError_t e = launch_dependent(moe_gather_kernel, (unsigned)rows, 256, 0, stream, (const bf16*)x,
+                                     (const int*)perm, top, (bf16*)x_sorted, width);
+    if (e != cudaSuccess) return (int)e;
+    int code = nnis_gemm_tc_grouped(x_sorted, w_gu, up, rows, 2 * ff, width, experts, tile_expert, 0, sm_count, status,
+                                    pdl, stream);
+    if (code != NNIS_OK) return code;
+    e = launch_dependent(moe_gated_act_kernel, (unsigned)rows, 256, 0, stream, (const float*)up, (const int*)perm,
+                         weights, (bf16*)act, ff);
+    if (e != cudaSuccess) return (int)e;
+    code = nnis_gemm_tc_grouped(act, w_down, y, rows, width, ff, experts, tile_expert, 0, sm_count, status, pdl,
+                                stream);
+    if (code != NNIS_OK) return code;
+    moe_combine_kernel<<<n_tokens, 256, 0, stream>>>(y, place, (const float*)nullptr, residual, width, top);
     NNIS_RETURN_LAUNCH();
 }

@@ -1588,3 +1588,32 @@ def moe_grouped_gated(h: torch.Tensor, w_gu: torch.Tensor, w_down: torch.Tensor,
     _check(_lib().nnis_moe_grouped_gated(_ptr(h), _ptr(w_gu), _ptr(w_down), _ptr(ids), _ptr(weights), _ptr(perm),
                                          _ptr(place), _ptr(tile_expert), _ptr(act), _ptr(y), _ptr(residual), n, width,
                                          ff, experts, top, _stream()), "moe_grouped_gated", 4)
+
+
+def moe_grouped_gated_tc(h: torch.Tensor, w_gu: torch.Tensor, w_down: torch.Tensor, ids: torch.Tensor,
+                         weights: torch.Tensor, perm: torch.Tensor, place: torch.Tensor, tile_expert: torch.Tensor,
+                         x_sorted: torch.Tensor, up: torch.Tensor, act: torch.Tensor, y: torch.Tensor,
+                         residual: torch.Tensor, top: int) -> None:
+    """``moe_grouped_gated`` with both products on the tcgen05 kernel: runs padded to tiles of 128 rows
+    (``moe_grouped_tc_tiles``); ``up`` float32 [tiles * 128, 2 ff] takes the first product's sums, a row-wise
+    kernel applies score and activation."""
+    _cuda(h, w_gu, w_down, ids, weights, perm, place, tile_expert, x_sorted, up, act, y, residual)
+    n, width = h.shape
+    experts, ff2, _ = w_gu.shape
+    ff = ff2 // 2
+    rows = moe_grouped_tc_tiles(n * top, experts) * 128
+    _need(h.dtype == w_gu.dtype == w_down.dtype == act.dtype == x_sorted.dtype == torch.bfloat16,
+          "moe_grouped_gated_tc: bfloat16")
+    _need(tuple(w_gu.shape) == (experts, 2 * ff, width) and tuple(w_down.shape) == (experts, width, ff),
+          "moe_grouped_gated_tc: stacked weights")
+    _need(moe_grouped_takes(width, ff, experts) and TC_GEMM, "moe_grouped_gated_tc: sizes not taken")
+    _need(perm.dtype == place.dtype == tile_expert.dtype == ids.dtype == torch.int32 and perm.numel() >= rows
+          and place.numel() >= n * top and tile_expert.numel() >= rows // 128, "moe_grouped_gated_tc: int32 scratch")
+    _need(x_sorted.numel() >= rows * width and act.numel() >= rows * ff and y.dtype == up.dtype == torch.float32
+          and y.numel() >= rows * width and up.numel() >= rows * 2 * ff, "moe_grouped_gated_tc: scratch")
+    _need(residual.dtype == torch.float32 and tuple(residual.shape) == (n, width), "moe_grouped_gated_tc: residual")
+    _check(_lib().nnis_moe_grouped_gated_tc(_ptr(h), _ptr(w_gu), _ptr(w_down), _ptr(ids), _ptr(weights), _ptr(perm),
+                                            _ptr(place), _ptr(tile_expert), _ptr(x_sorted), _ptr(up), _ptr(act),
+                                            _ptr(y), _ptr(residual), n, width, ff, experts, top,
+                                            sm_count(h.device), _ptr(status_word(h.device)), PDL, _stream()),
+           "moe_grouped_gated_tc", 6)

@@ -21,7 +21,9 @@ with x = score * h: the router's scores are sigmoid(z) (``scores`` "sigmoid"), u
 are, and they multiply the expert's INPUT (``weight_on`` "input"); the output is the plain sum
 of the chosen experts'.  Gate and up are stacked per expert with their rows interleaved ([experts,
 2 ff, width]); the score multiplies their float32 sums, which is the product with score * h.
-Prompt steps in bfloat16 sort the pairs by expert and run grouped products on mma.sync tiles.
+Prompt steps in bfloat16 sort the pairs by expert and run grouped products: on mma.sync tiles
+(score and activation in the first product's epilogue) where an expert gets few rows, on the
+tcgen05 kernel (float32 sums, then a row-wise kernel for score and activation) where it gets many.
 
 params: hidden_size, experts, top, ff, shared_ff (0: no shared expert), activation
 ("relu2" | "silu_gated"), scores ("softmax" over the chosen logits | "sigmoid"), weight_on
@@ -135,8 +137,22 @@ class MoEFeedForward(Part):
         weights = ws.get("moe_weights", (n, self.top), torch.float32)
         ops.moe_route(x, self.w_router, self.b_router, ctx.token_pos, ids, weights, self.top,
                       sigmoid_scores=self.scores == "sigmoid")
-        if self.gated and self.dtype == torch.bfloat16 and not ctx.decode and n >= self.GROUPED_FROM \
-                and ops.MOE_GROUPED and ops.moe_grouped_takes(self.hidden, self.ff, self.experts):
+        grouped_gated = self.gated and self.dtype == torch.bfloat16 and not ctx.decode and n >= self.GROUPED_FROM \
+            and ops.MOE_GROUPED and ops.moe_grouped_takes(self.hidden, self.ff, self.experts)
+        if grouped_gated and ops.TC_GEMM and n * self.top >= self.TCGEN05_ROWS * self.experts:
+            # many tokens an expert: runs padded to 128 rows, both products on the tcgen05 kernel
+            tiles = ops.moe_grouped_tc_tiles(n * self.top, self.experts)
+            ops.moe_grouped_gated_tc(x, self.w_up, self.w_down, ids, weights,
+                                     ws.get("moe_perm", (tiles * 128,), torch.int32),
+                                     ws.get("moe_place", (n * self.top,), torch.int32),
+                                     ws.get("moe_tile_expert", (tiles,), torch.int32),
+                                     ws.get("moe_x_sorted", (tiles * 128, self.hidden), self.dtype),
+                                     ws.get("moe_up_sorted", (tiles * 128, 2 * self.ff), torch.float32),
+                                     ws.get("moe_act_sorted", (tiles * 128, self.ff), self.dtype),
+                                     ws.get("moe_y_sorted", (tiles * 128, self.hidden), torch.float32), residual,
+                                     self.top)
+            return
+        if grouped_gated:
             tiles = ops.moe_grouped_tiles(n * self.top, self.experts)
             ops.moe_grouped_gated(x, self.w_up, self.w_down, ids, weights,
                                   ws.get("moe_perm", (tiles * 64,), torch.int32),
