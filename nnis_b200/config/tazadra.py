@@ -235,7 +235,8 @@ class TazadraConfig:
             if mlp is not None:
                 parts["ffn_norm"] = self._norm("norm2")
             layers.append(LayerSpec(prefix=f"l{i}", block="branch_norm", parts=parts,
-                                    params={"residual_mult": self.residual_mult}))
+                                    params={"residual_mult": self.residual_mult,
+                                            "tolerated": () if mlp is not None else ("norm2",)}))
             source = layer.mixer.get("kv_from") if layer.type == "attention" else None
             schedule.append(ScheduleEntry(i, cache_of=source))
         spec = ModelSpec(

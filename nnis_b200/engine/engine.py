@@ -104,6 +104,8 @@ class Engine:
         compute = _DTYPES[dtype]
         kept = {}
         for name, ws in wanted.items():
+            if ws.role == "unused":
+                continue
             t = tensors[name]
             if not shape_fits(tuple(t.shape), tuple(ws.shape)):
                 raise ValueError(f"{name}: shape {list(t.shape)}, expected {list(ws.shape)}")

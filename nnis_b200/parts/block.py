@@ -208,6 +208,13 @@ class BranchNormBlock(Block):
     def parts(self):
         return tuple(p for p in (self.mixer, self.mixer_norm, self.ffn, self.ffn_norm) if p is not None)
 
+    def weight_specs(self) -> Dict[str, WeightSpec]:
+        specs = super().weight_specs()
+        # a layer without a feed-forward has no use for the second norm; a folder may still hold it
+        for stem in self.spec.params.get("tolerated", ()):
+            specs.setdefault(f"{self.spec.prefix}.{stem}", WeightSpec((-1,), "unused"))
+        return specs
+
     def _close(self, branch, norm, hidden, ctx, n, width):
         """hidden += m * norm(branch); returns what the next sub-layer reads."""
         if self.dtype == torch.float32:

@@ -40,7 +40,7 @@ class WeightError(ValueError):
 @dataclass(frozen=True)
 class WeightSpec:
     shape: Tuple[int, ...]  # an extent of -1: whatever the stored tensor has there
-    role: str  # "matrix" | "vector" | "table" (integer)
+    role: str  # "matrix" | "vector" | "table" (integer) | "unused" (may be stored; never read, never missed)
     init: str = "normal"  # random mode: "normal" around 0, "ones" around 1
     fan_in: int = 0  # random mode: inputs summed per output (0: not a projection)
 
@@ -114,12 +114,14 @@ def _open_and_check(model_dir: str, wanted: Mapping[str, WeightSpec]):
                 if name in where:
                     duplicate.append(name)
                 where[name] = f
-        missing = sorted(n for n in wanted if n not in where)
+        missing = sorted(n for n, spec in wanted.items() if n not in where and spec.role != "unused")
         ignored = sorted(n for n in where if n not in wanted and any(p.match(n) for p in _IGNORED))
         unexpected = sorted(n for n in where if n not in wanted and n not in ignored)
         wrong: List[str] = []
         for name, spec in wanted.items():
             if name not in where:
+                continue
+            if spec.role == "unused":
                 continue
             dtype, shape = where[name].meta(name)
             if not shape_fits(shape, spec.shape):
@@ -155,6 +157,8 @@ def check_weights(model_dir: str, wanted: Mapping[str, WeightSpec]) -> Dict[str,
     try:
         dtypes, stored_bytes = set(), 0
         for name in wanted:
+            if name not in where:  # (a tensor that may be stored and is not)
+                continue
             dtype, shape = where[name].meta(name)
             dtypes.add(str(dtype).replace("torch.", ""))
             count = 1
@@ -175,6 +179,8 @@ def load_weights(model_dir: str, wanted: Mapping[str, WeightSpec], compute_dtype
     try:
         out: Dict[str, torch.Tensor] = {}
         for name, spec in wanted.items():
+            if spec.role == "unused":
+                continue
             t = where[name].tensor(name)
             out[name] = t.to(_kept_dtype(spec.role, t.dtype, compute_dtype)).to(device).contiguous()
         return out

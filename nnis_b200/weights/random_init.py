@@ -47,6 +47,8 @@ def random_tensors(wanted: Mapping[str, WeightSpec], seed: int, std: float = 0.0
             raise ValueError(f"{name}: integer tables have no random mode")
         gen = torch.Generator(device="cpu")
         gen.manual_seed(tensor_seed(seed, name))
+        if spec.role == "unused":
+            continue
         if any(extent < 0 for extent in spec.shape):
             raise ValueError(f"{name}: the configuration leaves an extent of {list(spec.shape)} to the stored "
                              f"tensor; random weights need it named")

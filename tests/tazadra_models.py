@@ -82,7 +82,8 @@ ODD = config(211, 76, 1e-6, 1.0, None, [
 ONLY_ATTENTION = config(150, 64, 1e-5, 0.5, None, [
     layer(attention(4, 2, 16, 24, 8, 0.5, base=100.0, softcap=10.0, chunk=50), None)])
 ONLY_WKV = config(150, 64, 1e-5, 0.5, None, [layer(wkv(2, 32, 16), None)])
-WIDE_WKV = config(150, 64, 1e-5, 0.8, None, [layer(wkv(2, 72, 10), None), layer(wkv(1, 136, 4), None)])
+WIDE_WKV = config(150, 64, 1e-5, 0.8, None, [layer(wkv(2, 72, 10), None), layer(wkv(1, 136, 4), None),
+                                             layer(wkv(1, 256, 3), None)])
 ONLY_MAMBA = config(150, 64, 1e-5, 0.5, None, [layer(mamba(96, 16, 4, 4), None)])
 WIDE_MAMBA = config(150, 48, 1e-5, 0.9, None, [layer(mamba(72, 70, 5, 1), None), layer(mamba(40, 130, 2, 3), None)])
 ONLY_DENSE = config(150, 72, 1e-5, 0.5, 30.0, [layer(wkv(1, 8, 4), dense(88, 0.8))])

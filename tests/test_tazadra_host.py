@@ -63,8 +63,9 @@ def test_tensor_names_and_the_free_extent(tmp_path):
                  "l0.mix.g", "l0.mlp.router", "l0.mlp.e5.gate", "l1.mix.mu.w", "l1.mix.w0", "l1.mix.u", "l1.mlp.up",
                  "l2.mix.conv", "l2.mix.conv.b", "l2.mix.A_log", "l2.mix.dt.b", "l2.mix.D", "l3.mix.q", "l4.norm1"):
         assert name in want, name
-    for name in ("l3.mix.k", "l3.mix.v", "l3.mix.k.norm", "l4.norm2", "l0.mix.q.weight"):
+    for name in ("l3.mix.k", "l3.mix.v", "l3.mix.k.norm", "l0.mix.q.weight"):
         assert name not in want, name
+    assert want["l4.norm2"].role == "unused"  # (a layer without a feed-forward neither reads nor misses it)
     assert want["l0.mix.v"].shape == (2 * 16, 96) and want["l0.mix.g"].shape == (4, 96)
     assert want["l2.mix.x"].shape == (6 + 2 * 12, 80) and want["l2.mix.conv"].shape == (80, 3)
     assert want["l1.mix.u"].shape == (3, 16) and want["l1.mix.w1"].shape == (12, 96)
@@ -226,3 +227,27 @@ def test_plain_forward_runs_every_configuration_and_prefixes_agree(tmp_path):
         whole = P.forward(read_config(d), w, toks)
         part = P.forward(read_config(d), w, toks[:17])
         assert torch.isfinite(whole).all() and torch.allclose(whole[:17], part, atol=1e-9), name
+
+
+def test_a_layer_without_feed_forward_tolerates_a_stored_second_norm(tmp_path):
+    """The folder may hold the second norm of a layer that has no feed-forward: it is neither read nor
+    missed, and any other stranger is still refused."""
+    from safetensors.torch import load_file, save_file
+    from nnis_b200.config import read_config as typed_config
+    from nnis_b200.engine.model import DecoderModel
+    from nnis_b200.weights.loader import WeightError, check_weights
+    import os
+    d = make_model(str(tmp_path / "m"), MIXED, seed=1)
+    wanted = DecoderModel.weight_specs_of(typed_config(d).to_spec())
+    assert wanted["l4.norm2"].role == "unused" and "l3.norm2" in wanted and wanted["l3.norm2"].role == "vector"
+    path = os.path.join(d, "model.safetensors")
+    w = load_file(path)
+    assert "l4.norm2" not in w
+    check_weights(d, wanted)
+    w["l4.norm2"] = torch.ones(96, dtype=torch.bfloat16)
+    save_file(w, path)
+    check_weights(d, wanted)
+    w["l4.norm3"] = torch.ones(96, dtype=torch.bfloat16)
+    save_file(w, path)
+    with pytest.raises(WeightError, match="unexpected"):
+        check_weights(d, wanted)
