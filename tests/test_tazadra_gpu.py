@@ -256,6 +256,40 @@ def test_a_slot_used_again_starts_from_nothing(models):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+def test_a_prompt_shape_that_recurs_is_captured_and_replayed(models, dtype):
+    """A large prompt step whose shape comes a second time is recorded as a CUDA graph and replayed from
+    the third time on: the recurrent layers' states, the runs' tables and the branch buffers must all
+    live where the graph expects them.  Other tokens every time, the same shape."""
+    from nnis_b200.engine import Engine, SequenceStep
+    engine = Engine.from_dir(models["mixed"], dtype=dtype, max_tokens=64 * 64)
+    vocab = read_config(models["mixed"])["vocab"]
+    rng = random.Random(77)
+    graphs = []
+    for round_ in range(4):
+        a, b = random_tokens(rng, 300, vocab), random_tokens(rng, 40, vocab)
+        slots = [engine.acquire_slot(), engine.acquire_slot()]
+        got = engine.step([SequenceStep(slots[0], a[:290], [0, 150, 289]), SequenceStep(slots[1], b[:30], [29])]).cpu().numpy()
+        more = engine.step([SequenceStep(slots[0], a[290:291], [0]), SequenceStep(slots[1], b[30:31], [0])]).cpu().numpy()
+        for s_ in slots:
+            engine.release_slot(s_)
+        graphs.append(len(engine._step_graphs))
+        keep_a, keep_b = clear_calls(models, "mixed", dtype, a), clear_calls(models, "mixed", dtype, b)
+        rows = [(a, 0, got[0], keep_a), (a, 150, got[1], keep_a), (a, 289, got[2], keep_a), (b, 29, got[3], keep_b),
+                (a, 290, more[0], keep_a), (b, 30, more[1], keep_b)]
+        missed = 0
+        for toks, pos, row, keep in rows:
+            if not bool(keep[pos]):
+                continue
+            want = plain_logits(models, "mixed", dtype, toks)[pos][None, :]
+            if dtype == "float32":
+                check_logits(row[None, :], want, dtype, f"captured step, round {round_}, position {pos}")
+            else:
+                missed += rows_beyond_the_bound(row[None, :], want)
+        assert missed <= 1, (round_, missed)
+    assert graphs == [0, 1, 1, 1], graphs
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
 def test_long_decoding_over_page_and_chunk_borders(models, dtype, tmp_path):
     vocab = read_config(models["mixed"])["vocab"]
     toks = random_tokens(random.Random(21), 5 + 200, vocab)
