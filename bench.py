@@ -267,9 +267,9 @@ def design_configs(size: str):
     nafezen = {"architecture": "Nafezen", "vocab": 32768, "width": width, "norm": {"eps": 1e-5, "groups": 4},
                "layers": [{"type": t, "mixer": m, "mlp": f} for t, m, f in (pattern[i % 4] for i in range(layers))]}
     attention = {"heads": heads, "kv_heads": heads // 4, "dim": dim, "vdim": dim, "scale": dim ** -0.5,
-                 "softcap": 30.0, "mask": {"size": 1024},
-                 "rot": {"base": 100000.0, "dims": dim,
-                         "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 1024}}}
+                 "softcap": 50.0, "mask": {"size": 1024},
+                 "rot": {"base": 500000.0, "dims": dim,
+                         "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}}
     wkv = {"heads": width // 64, "dim": 64, "decay_rank": 64}
     scan = {"inner": 2 * width, "state": 16, "dt_rank": width // 16, "conv": 4}
     t_dense = {"kind": "dense", "ff": ff, "limit": 7.0}
@@ -280,7 +280,7 @@ def design_configs(size: str):
                             ("attention", {**attention, "kv_from": i - 3}, t_dense)][i % 4]
         t_layers.append({"type": kind, "mixer": mixer, "mlp": mlp})
     tazadra = {"architecture": "Tazadra", "vocab": 32768, "width": width, "norm": {"eps": 1e-5},
-               "residual_mult": 0.5, "logit_softcap": 30.0, "layers": t_layers}
+               "residual_mult": 0.7, "logit_softcap": 40.0, "layers": t_layers}
     return llama, nafezen, tazadra
 
 

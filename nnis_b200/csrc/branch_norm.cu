@@ -4,7 +4,8 @@
 //                    sub-layers of such a block read (they read the stream itself)
 //   norm_scale_add   hidden += mult * rmsnorm(branch) * w, where `branch` is what a
 //                    sub-layer added up in float32; optionally also the new rows in the
-//                    operand dtype, for the sub-layer that reads them next
+//                    operand dtype, for the sub-layer that reads them next; optionally the
+//                    branch rows are left zero, ready for the next sub-layer to add into
 //   glu_clamp        the feed-forward activation g' sigmoid(alpha g') (u' + 1) with
 //                    g' = min(g, limit), u' = clamp(u, -limit, limit)
 //   tanh_rows        tanh of float32 rows, rounded once to the operand dtype
@@ -31,13 +32,13 @@ __global__ void cast_rows_kernel(const float* __restrict__ x, T* __restrict__ ou
 // a CTA of 256 threads per row
 template <typename T>
 __global__ void __launch_bounds__(256)
-norm_scale_add_kernel(const float* __restrict__ branch, const float* __restrict__ w,
-                      float* __restrict__ hidden, T* __restrict__ out, int width, float eps, float mult) {
+norm_scale_add_kernel(float* __restrict__ branch, const float* __restrict__ w,
+                      float* __restrict__ hidden, T* __restrict__ out, int width, float eps, float mult, int clear) {
     __shared__ float red[8];
     pdl_wait();
     pdl_launch_dependents();
     const size_t row = blockIdx.x;
-    const float* b = branch + row * width;
+    float* b = branch + row * width;
     float ss = 0.f;
     for (int i = threadIdx.x; i < width; i += 256) ss = fmaf(b[i], b[i], ss);
     ss = warp_sum(ss);
@@ -52,6 +53,7 @@ norm_scale_add_kernel(const float* __restrict__ branch, const float* __restrict_
         float v = fmaf(b[i] * s, w[i], h[i]);
         h[i] = v;
         if (out) out[row * width + i] = from_float<T>(v);
+        if (clear) b[i] = 0.f;
     }
 }
 
@@ -102,17 +104,17 @@ NNIS_API int nnis_cast_rows(const float* x, void* out, int out_dtype, long long 
     return e == cudaSuccess ? NNIS_OK : (int)e;
 }
 
-// out may be null (no copy in the operand dtype is wanted)
-NNIS_API int nnis_norm_scale_add(const float* branch, const float* w, float* hidden, void* out, int out_dtype,
-                                 int n_rows, int width, float eps, float mult, cudaStream_t stream) {
+// out may be null (no copy in the operand dtype is wanted); clear: the branch rows are zero afterwards
+NNIS_API int nnis_norm_scale_add(float* branch, const float* w, float* hidden, void* out, int out_dtype,
+                                 int n_rows, int width, float eps, float mult, int clear, cudaStream_t stream) {
     if (n_rows <= 0 || width <= 0 || !(eps > 0.f) || !branch || !w || !hidden) return NNIS_ERR_ARGUMENT;
     cudaError_t e;
     if (out_dtype == NNIS_DTYPE_F32)
         e = launch_dependent(norm_scale_add_kernel<float>, (unsigned)n_rows, 256, 0, stream, branch, w, hidden,
-                             (float*)out, width, eps, mult);
+                             (float*)out, width, eps, mult, clear);
     else if (out_dtype == NNIS_DTYPE_BF16)
         e = launch_dependent(norm_scale_add_kernel<bf16>, (unsigned)n_rows, 256, 0, stream, branch, w, hidden,
-                             (bf16*)out, width, eps, mult);
+                             (bf16*)out, width, eps, mult, clear);
     else
         return NNIS_ERR_UNSUPPORTED;
     return e == cudaSuccess ? NNIS_OK : (int)e;

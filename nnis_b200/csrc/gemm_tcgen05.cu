@@ -66,6 +66,9 @@ struct GemmArgs {
     const int* tile_expert;
     int expert_rows;
     int square_relu;  // the epilogue stores relu(x)^2 (the experts' activation) instead of x
+    // GEMM_GATED with glu_limit > 0: the clamped form g' sigmoid(glu_alpha g') (u' + 1) with
+    // g' = min(gate, limit), u' = up clamped to [-limit, limit], instead of silu(gate) * up
+    float glu_limit, glu_alpha;
 };
 
 // Two CTAs share an SM when their stages leave room for it.
@@ -445,7 +448,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                         // relative error about 1e-7 each): the exact forms cost the
                         // epilogue twice the time of the products
                         float e, r;
-                        asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(gv * -1.4426950408889634f));
+                        float slope = -1.4426950408889634f;
+                        if (g.glu_limit > 0.f) {  // the clamped form, sigmoid of alpha * g
+                            gv = fminf(gv, g.glu_limit);
+                            uv = fminf(fmaxf(uv, -g.glu_limit), g.glu_limit) + 1.0f;
+                            slope *= g.glu_alpha;
+                        }
+                        asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(gv * slope));
                         asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(1.0f + e));
                         f[i] = gv * r * uv;
                     }
@@ -590,13 +599,13 @@ NNIS_API int nnis_gemm_tc_splits(int M, int N, int K, int sm_count, long long* f
 // zero before the first launch; the kernel leaves them zero) are optional: with them the
 // adding mode cuts a long K among several CTAs per tile where tiles are few (see
 // nnis_gemm_tc_splits).
-NNIS_API int nnis_gemm_tc(const void* A, const void* W, const float* bias, void* C, int M, int N,
-                          int K, int mode, const int* token_pos, const int* token_seq,
-                          const int* page_table, int table_cols, const float* cos_t,
-                          const float* sin_t, void* k_cache, void* v_cache, int nq, int nkv, int d,
-                          int page_size, float* split_scratch, long long split_floats,
-                          unsigned* split_tickets, int split_tiles, int sm_count, int* status, int pdl,
-                          cudaStream_t stream) {
+static int gemm_tc_run(const void* A, const void* W, const float* bias, void* C, int M, int N,
+                       int K, int mode, const int* token_pos, const int* token_seq,
+                       const int* page_table, int table_cols, const float* cos_t,
+                       const float* sin_t, void* k_cache, void* v_cache, int nq, int nkv, int d,
+                       int page_size, float* split_scratch, long long split_floats,
+                       unsigned* split_tickets, int split_tiles, int sm_count, int* status, int pdl,
+                       cudaStream_t stream, float glu_limit, float glu_alpha) {
     using namespace nnis;
     if (M <= 0 || N <= 0 || K <= 0 || !A || !W || !C || mode < 0 || mode > 4) return NNIS_ERR_ARGUMENT;
     if (K % 8) return NNIS_ERR_UNSUPPORTED;
@@ -610,6 +619,7 @@ NNIS_API int nnis_gemm_tc(const void* A, const void* W, const float* bias, void*
     g.v_cache = (bf16*)v_cache; g.nq = nq; g.nkv = nkv; g.d = d; g.page_size = page_size;
     g.k_splits = 1; g.split_scratch = nullptr; g.split_tickets = nullptr;
     g.tile_expert = nullptr; g.expert_rows = 0; g.square_relu = 0;
+    g.glu_limit = glu_limit; g.glu_alpha = glu_alpha;
     static const char* const kNames[] = {"gemm store", "gemm store_f32", "gemm add_f32", "gemm gated", "gemm qkv"};
     g.trace = trace_slot(mode >= 0 && mode <= 4 ? kNames[mode] : "gemm");
     int sms = sm_count > 0 ? sm_count : 148;
@@ -672,6 +682,28 @@ NNIS_API int nnis_gemm_tc(const void* A, const void* W, const float* bias, void*
 #undef NNIS_GEMM_TC64
 #undef NNIS_GEMM_TC128
 #undef NNIS_GEMM_TC
+}
+
+NNIS_API int nnis_gemm_tc(const void* A, const void* W, const float* bias, void* C, int M, int N,
+                          int K, int mode, const int* token_pos, const int* token_seq,
+                          const int* page_table, int table_cols, const float* cos_t,
+                          const float* sin_t, void* k_cache, void* v_cache, int nq, int nkv, int d,
+                          int page_size, float* split_scratch, long long split_floats,
+                          unsigned* split_tickets, int split_tiles, int sm_count, int* status, int pdl,
+                          cudaStream_t stream) {
+    return gemm_tc_run(A, W, bias, C, M, N, K, mode, token_pos, token_seq, page_table, table_cols, cos_t, sin_t,
+                       k_cache, v_cache, nq, nkv, d, page_size, split_scratch, split_floats, split_tickets,
+                       split_tiles, sm_count, status, pdl, stream, 0.f, 0.f);
+}
+
+// The gated product (mode 3) with the clamped activation in its epilogue: out [M, N / 2] =
+// bf16(g' sigmoid(alpha g') (u' + 1)), g' = min(gate, limit), u' = up clamped to [-limit, limit].
+NNIS_API int nnis_gemm_tc_glu_clamp(const void* A, const void* W, const float* bias, void* C, int M, int N, int K,
+                                    float limit, float alpha, int sm_count, int* status, int pdl,
+                                    cudaStream_t stream) {
+    if (!(limit > 0.f)) return NNIS_ERR_ARGUMENT;
+    return gemm_tc_run(A, W, bias, C, M, N, K, 3, nullptr, nullptr, nullptr, 0, nullptr, nullptr, nullptr, nullptr,
+                       0, 0, 0, 0, nullptr, 0, nullptr, 0, sm_count, status, pdl, stream, limit, alpha);
 }
 
 // Grouped product on the tensor cores: C[M, N] = A[M, K] . W[tile_expert[m / 128]]^T with

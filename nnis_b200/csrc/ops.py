@@ -870,6 +870,25 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out:
 
 
 # Whether the adding product may cut a long K among CTAs (few tiles): parts/linear.py asks.
+def gemm_tc_glu_clamp(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor,
+                      limit: float, alpha: float) -> None:
+    """The gated tensor-core product with the clamped activation in its epilogue: w = [gate; up] rows,
+    out bfloat16 [m, n / 2] = g' sigmoid(alpha g') (u' + 1), g' = min(gate, limit), u' = up clamped to
+    [-limit, limit]."""
+    _cuda(a, w, bias, out)
+    m, k = a.shape
+    n = w.shape[0]
+    _need(a.dtype == w.dtype == torch.bfloat16 and w.shape[1] == k, "gemm_tc_glu_clamp: bfloat16 a [m, k], w [n, k]")
+    _need(gemm_tc_takes(m, n, k) and limit > 0, f"gemm_tc_glu_clamp: shape m={m} n={n} k={k} is not taken")
+    _need(n % 2 == 0 and out.dtype == torch.bfloat16 and tuple(out.shape) == (m, n // 2),
+          "gemm_tc_glu_clamp: out bfloat16 [m, n / 2]")
+    if bias is not None:
+        _need(bias.dtype == torch.float32 and bias.numel() == n, "gemm_tc_glu_clamp: bias float32 [n]")
+    _check(_lib().nnis_gemm_tc_glu_clamp(_ptr(a), _ptr(w), _ptr(bias), _ptr(out), m, n, k, ctypes.c_float(limit),
+                                         ctypes.c_float(alpha), sm_count(a.device), _ptr(status_word(a.device)),
+                                         PDL, _stream()), "gemm_tc_glu_clamp")
+
+
 GEMM_SPLIT_K = os.environ.get("NNIS_GEMM_SPLIT_K", "1") == "1"
 
 
@@ -1277,9 +1296,9 @@ def cast_rows(x: torch.Tensor, out: torch.Tensor) -> None:
 
 
 def norm_scale_add(branch: torch.Tensor, weight: torch.Tensor, eps: float, mult: float,
-                   hidden: torch.Tensor, out: Optional[torch.Tensor] = None) -> None:
+                   hidden: torch.Tensor, out: Optional[torch.Tensor] = None, clear: bool = False) -> None:
     """hidden += mult * rmsnorm(branch) * weight (all float32); ``out``, if given, receives the
-    new rows of hidden in its own dtype."""
+    new rows of hidden in its own dtype; with ``clear`` the rows of ``branch`` are zero afterwards."""
     _cuda(branch, weight, hidden, out)
     n, width = hidden.shape
     _need(branch.dtype == hidden.dtype == weight.dtype == torch.float32 and tuple(branch.shape) == (n, width)
@@ -1287,7 +1306,8 @@ def norm_scale_add(branch: torch.Tensor, weight: torch.Tensor, eps: float, mult:
     _need(out is None or tuple(out.shape) == (n, width), "norm_scale_add: out [n, width]")
     _check(_lib().nnis_norm_scale_add(_ptr(branch), _ptr(weight), _ptr(hidden), _ptr(out),
                                       code_of(out.dtype) if out is not None else F32, n, width,
-                                      ctypes.c_float(eps), ctypes.c_float(mult), _stream()), "norm_scale_add")
+                                      ctypes.c_float(eps), ctypes.c_float(mult), 1 if clear else 0, _stream()),
+           "norm_scale_add")
 
 
 def glu_clamp(gate_up: torch.Tensor, out: torch.Tensor, limit: float, alpha: float) -> None:

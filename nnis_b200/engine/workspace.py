@@ -60,6 +60,22 @@ class Workspace:
             self._buffers[key] = buf
         return buf[:count].view(*shape)
 
+    def kept_zero(self, name: str, shape, dtype: torch.dtype) -> torch.Tensor:
+        """Like ``get``, for a buffer whose users leave every value they touched at zero again
+        (an accumulator that the kernel which reads it last clears): zero when first handed out
+        and when it has to grow, so that it needs no fill between uses."""
+        count = 1
+        for s in shape:
+            count *= int(s)
+        key = (name + "#kept_zero", dtype)
+        buf = self._buffers.get(key)
+        if buf is None or buf.numel() < count:
+            if self.frozen:
+                raise RuntimeError(f"workspace buffer {name!r} would move after graph capture")
+            buf = torch.zeros(max(count, 1), dtype=dtype, device=self.device)
+            self._buffers[key] = buf
+        return buf[:count].view(*shape)
+
     def zeros(self, name: str, shape, dtype: torch.dtype) -> torch.Tensor:
         """A buffer that is zero when first handed out and that its users leave
         zero (tickets of kernels that reset them); never moved once made."""

@@ -189,8 +189,8 @@ class BranchNormBlock(Block):
     """A norm on each sub-layer's output and a multiplier: with m = ``residual_mult``,
     x += m * norm1(mixer(x)), then x += m * norm2(ffn(x)).  The sub-layers read x itself (in
     the operand dtype); each adds its output up in a zeroed float32 branch buffer, as it would
-    into the residual stream, and one kernel norms that buffer, scales it and adds it to the
-    stream.  In bfloat16 the same kernel leaves the new rows of the stream in bfloat16 for the
+    into the residual stream, and one kernel norms that buffer, scales it, adds it to the
+    stream and leaves the buffer zero again.  In bfloat16 the same kernel leaves the new rows of the stream in bfloat16 for the
     sub-layer that reads them next (``ctx.hidden_copy`` across blocks).  Roles: mixer,
     mixer_norm and, optionally, ffn with ffn_norm.  The norms are RMS norms (``rmsnorm``)."""
 
@@ -218,12 +218,12 @@ class BranchNormBlock(Block):
     def _close(self, branch, norm, hidden, ctx, n, width):
         """hidden += m * norm(branch); returns what the next sub-layer reads."""
         if self.dtype == torch.float32:
-            ops.norm_scale_add(branch, norm.weight, norm.eps, self.mult, hidden)
+            ops.norm_scale_add(branch, norm.weight, norm.eps, self.mult, hidden, clear=True)
             return hidden
         # (two buffers in turn: the sub-layer that just ran may still be the reader of one)
         ctx.copy_turn = 1 - getattr(ctx, "copy_turn", 0)
         x = ctx.workspace.get(f"stream_copy{ctx.copy_turn}", (n, width), self.dtype)
-        ops.norm_scale_add(branch, norm.weight, norm.eps, self.mult, hidden, x)
+        ops.norm_scale_add(branch, norm.weight, norm.eps, self.mult, hidden, x, clear=True)
         return x
 
     def forward(self, hidden: torch.Tensor, ctx, cache) -> None:
@@ -236,12 +236,15 @@ class BranchNormBlock(Block):
         elif x is None:
             x = ws.get("stream_copy_first", (n, width), self.dtype)
             ops.cast_rows(hidden, x)
-        branch = ws.get("branch_out", (n, width), torch.float32)
-        branch.zero_()
+        # the kernel that norms the branch buffer leaves it zero for the next sub-layer; steps of
+        # single tokens (a chain of short launches, mostly inside a captured graph) rely on that,
+        # prompt steps fill it anyway (a step that was abandoned half-way may have left anything)
+        branch = ws.kept_zero("branch_out", (n, width), torch.float32)
+        if not ctx.decode:
+            branch.zero_()
         self.mixer.forward(x, ctx, branch, cache)
         x = self._close(branch, self.mixer_norm, hidden, ctx, n, width)
         if self.ffn is not None:
-            branch.zero_()
             self.ffn.forward(x, ctx, branch)
             x = self._close(branch, self.ffn_norm, hidden, ctx, n, width)
         ctx.hidden_copy = x if self.dtype != torch.float32 else None

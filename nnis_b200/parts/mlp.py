@@ -8,8 +8,8 @@ dtype.  Steps 14-18 of NNIS's token pass
 params: hidden_size, intermediate_size, activation, bias, names {gate, up, down}.
 Activations: "silu" (silu(gate) * up, fused into the products' epilogues where those
 exist) and "glu_clamp" with ``limit`` and ``alpha``: g' sigmoid(alpha g') (u' + 1) with
-g' = min(gate, limit), u' = up clamped to [-limit, limit] (a kernel of its own after the
-float32 product).
+g' = min(gate, limit), u' = up clamped to [-limit, limit] (in the tcgen05 product's epilogue where
+that product runs; a kernel of its own after a float32 product elsewhere).
 """
 from __future__ import annotations
 
@@ -111,6 +111,10 @@ class GatedMLP(Part):
                 and ops.gemm_tc_takes(n, 2 * self.inter, self.hidden):
             # tensor-core product with the activation in its epilogue
             ops.gemm_tc(x, self.w_gu, self.b_gu, act, ops.GEMM_GATED)
+        elif self.activation == "glu_clamp" and self.dtype == torch.bfloat16 \
+                and ops.gemm_tc_takes(n, 2 * self.inter, self.hidden):
+            # the same product with the clamped activation in its epilogue
+            ops.gemm_tc_glu_clamp(x, self.w_gu, self.b_gu, act, self.limit, self.alpha)
         else:
             gate_up = ws.get("gate_up", (n, 2 * self.inter), torch.float32)
             linear(x, self.w_gu, self.b_gu, gate_up, STORE_F32, decode=ctx.decode)

@@ -122,9 +122,13 @@ def test_norm_on_a_branch_activations_and_the_soft_cap():
         for dtype in (torch.float32, torch.bfloat16):
             h = hidden.to(dev).clone()
             out = torch.empty(n, width, dtype=dtype, device=dev)
-            ops.norm_scale_add(branch.to(dev), w.to(dev), 1e-5, 0.7, h, out)
+            b = branch.to(dev)
+            ops.norm_scale_add(b, w.to(dev), 1e-5, 0.7, h, out)
             assert torch.allclose(h.cpu().double(), want, atol=2e-5, rtol=1e-5)
-            assert torch.equal(out.cpu(), h.cpu().to(dtype))
+            assert torch.equal(out.cpu(), h.cpu().to(dtype)) and torch.equal(b.cpu(), branch)
+            h2 = hidden.to(dev).clone()
+            ops.norm_scale_add(b, w.to(dev), 1e-5, 0.7, h2, None, clear=True)  # the buffer is left zero
+            assert torch.equal(h2, h) and float(b.abs().max()) == 0.0
         x = torch.empty(n, width, dtype=torch.bfloat16, device=dev)
         ops.cast_rows(hidden.to(dev), x)
         assert torch.equal(x.cpu(), hidden.to(torch.bfloat16))
