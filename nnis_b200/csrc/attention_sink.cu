@@ -155,6 +155,7 @@ attn_sink_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, const T
                 const T* krow = k_cache + (size_t)row_index * dk;
                 float dot = 0.f;
                 const int d4 = (dk & 3) ? 0 : dk;
+#pragma unroll 8
                 for (int i = 0; i < d4; i += 4) {
                     float4 kv = load4(krow + i);
                     dot = fmaf(qs[i], kv.x, dot);
@@ -174,6 +175,7 @@ attn_sink_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, const T
 #pragma unroll
             for (int r = 0; r < R; ++r) acc[r] *= alpha;
             const int count = min(32, end - c);
+#pragma unroll 4
             for (int j = 0; j < count; ++j) {
                 float pj = __shfl_sync(0xffffffffu, p, j);
                 int rj = __shfl_sync(0xffffffffu, row_index, j);

@@ -71,10 +71,22 @@ moe_route_kernel(const T* __restrict__ h, const float* __restrict__ wr, const fl
         return;
     }
     const T* x = h + (size_t)n * width;
+    const bool by_four = (width & 3) == 0;  // rows of the router and of x start on 16- and 8-byte borders
     for (int e = warp; e < experts; e += 8) {  // a warp per expert, eight at a time
         const float* w = wr + (size_t)e * width;
         float acc = 0.f;
-        for (int i = lane; i < width; i += 32) acc = fmaf(w[i], to_float(x[i]), acc);
+        if (by_four) {  // several loads in flight per lane: the dot products are latency, not arithmetic
+#pragma unroll 4
+            for (int i = lane * 4; i < width; i += 128) {
+                float4 wv = load4(w + i), xv = load4(x + i);
+                acc = fmaf(wv.x, xv.x, acc);
+                acc = fmaf(wv.y, xv.y, acc);
+                acc = fmaf(wv.z, xv.z, acc);
+                acc = fmaf(wv.w, xv.w, acc);
+            }
+        } else {
+            for (int i = lane; i < width; i += 32) acc = fmaf(w[i], to_float(x[i]), acc);
+        }
         acc = warp_sum(acc);
         if (lane == 0) z[e] = acc + (br ? br[e] : 0.f);
     }
