@@ -82,7 +82,7 @@ selective_scan_kernel(const T* __restrict__ xc, const T* __restrict__ xz, const 
                       const int* __restrict__ seq_first_row, const int* __restrict__ seq_count,
                       const int* __restrict__ segments, int seg_len, float* __restrict__ seg_state,
                       float* __restrict__ seg_dt, T* __restrict__ y_out, int inner, int N, int NS, int taps) {
-    extern __shared__ float smem[];  // [kScanTile][2 N] B and C, then [kScanTile][3][channels of the CTA]
+    extern __shared__ __align__(16) float smem[];  // [kScanTile][2 N] B and C, then [kScanTile][3][channels of the CTA]
     pdl_wait();
     pdl_launch_dependents();
     const int unit = blockIdx.x;
@@ -151,11 +151,32 @@ selective_scan_kernel(const T* __restrict__ xc, const T* __restrict__ xz, const 
             const float* C = B + N;
             const float dx = dt * xv;
             float y = 0.f;
+            if ((N & 3) == 0) {  // B and C four values a load (their rows start on 16-byte borders)
 #pragma unroll
-            for (int i = 0; i < NL; ++i) {
-                if (n0 + i < N) {
-                    s[i] = fmaf(exp_for<T>(dt * a[i]), s[i], dx * B[i]);
-                    if (PASS != 1) y = fmaf(s[i], C[i], y);
+                for (int q = 0; q < NL / 4; ++q) {
+                    if (n0 + 4 * q < N) {
+                        const float4 b4 = reinterpret_cast<const float4*>(B)[q];
+                        const float bv[4] = {b4.x, b4.y, b4.z, b4.w};
+                        float cv[4] = {0.f, 0.f, 0.f, 0.f};
+                        if (PASS != 1) {
+                            const float4 c4 = reinterpret_cast<const float4*>(C)[q];
+                            cv[0] = c4.x, cv[1] = c4.y, cv[2] = c4.z, cv[3] = c4.w;
+                        }
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const int i = 4 * q + e;
+                            s[i] = fmaf(exp_for<T>(dt * a[i]), s[i], dx * bv[e]);
+                            if (PASS != 1) y = fmaf(s[i], cv[e], y);
+                        }
+                    }
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < NL; ++i) {
+                    if (n0 + i < N) {
+                        s[i] = fmaf(exp_for<T>(dt * a[i]), s[i], dx * B[i]);
+                        if (PASS != 1) y = fmaf(s[i], C[i], y);
+                    }
                 }
             }
             if (PASS == 1) {
@@ -206,11 +227,24 @@ scan_prefix_kernel(const float* __restrict__ a_log, float* __restrict__ state, c
     const float a = -expf(a_log[idx]);
     float* S = state + (size_t)seq_slots[seq] * inner * N + idx;
     float carry = *S;
-    for (int run = seq_first_segment[seq]; run < seq_first_segment[seq + 1]; ++run) {
-        float* at = seg_state + (size_t)run * inner * N + idx;
-        float added = *at;
-        *at = carry;
-        carry = fmaf(expf(a * seg_dt[(size_t)run * inner + c]), carry, added);
+    const int last = seq_first_segment[seq + 1];
+    const size_t per_run = (size_t)inner * N;
+    // four runs' values are asked for together: the walk itself is a chain, its loads need not be
+    for (int run = seq_first_segment[seq]; run < last; run += 4) {
+        float added[4], dt[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const bool in = run + q < last;
+            added[q] = in ? seg_state[(size_t)(run + q) * per_run + idx] : 0.f;
+            dt[q] = in ? seg_dt[(size_t)(run + q) * inner + c] : 0.f;
+        }
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            if (run + q < last) {
+                seg_state[(size_t)(run + q) * per_run + idx] = carry;
+                carry = fmaf(expf(a * dt[q]), carry, added[q]);
+            }
+        }
     }
     *S = carry;
 }

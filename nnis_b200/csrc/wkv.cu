@@ -89,16 +89,16 @@ wkv_scan_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __res
                 const int* __restrict__ seq_count, const int* __restrict__ segments, int seg_len,
                 float* __restrict__ seg_state, float* __restrict__ seg_logw, float* __restrict__ o_raw,
                 int heads, int dim, int KS, int TT) {
-    extern __shared__ float smem[];
+    extern __shared__ __align__(16) float smem[];
     pdl_wait();
     pdl_launch_dependents();
-    const int dimP = KS * KL;
+    const int dimP = KS * KL;         // (a multiple of eight: the four arrays below start on 16-byte borders)
     float* rs = smem;                 // [TT][dimP]
     float* ks = rs + TT * dimP;       // [TT][dimP]
     float* ws = ks + TT * dimP;       // [TT][dimP]
-    float* vs = ws + TT * dimP;       // [TT][dim]
-    float* us = vs + TT * dim;        // [dimP]
-    float* part = us + dimP;          // [TT][KS][dim]; PASS 1: [TT][dimP] logarithms of the decays
+    float* us = ws + TT * dimP;       // [dimP]
+    float* vs = us + dimP;            // [TT][dim]
+    float* part = vs + TT * dim;      // [TT][KS][dim]; PASS 1: [TT][dimP] logarithms of the decays
     const int unit = blockIdx.x, h = blockIdx.y;
     int first, count, slot;
     if (PASS != 0) {
@@ -143,15 +143,25 @@ wkv_scan_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __res
         __syncthreads();
         for (int t = 0; t < tn; ++t) {
             const float vj = vs[t * dim + j];
-            const float* rt = rs + t * dimP + k0;
-            const float* kt = ks + t * dimP + k0;
-            const float* wt = ws + t * dimP + k0;
+            // the tile's rows are read four values a load (every thread of a run reads the same ones)
+            const float4* rt = reinterpret_cast<const float4*>(rs + t * dimP + k0);
+            const float4* kt = reinterpret_cast<const float4*>(ks + t * dimP + k0);
+            const float4* wt = reinterpret_cast<const float4*>(ws + t * dimP + k0);
+            const float4* ut = reinterpret_cast<const float4*>(us + k0);
             float o = 0.f;
 #pragma unroll
-            for (int kk = 0; kk < KL; ++kk) {
-                float kv = kt[kk] * vj;
-                if (PASS != 1) o = fmaf(rt[kk], fmaf(us[k0 + kk], kv, s[kk]), o);
-                s[kk] = fmaf(wt[kk], s[kk], kv);
+            for (int kq = 0; kq < KL / 4; ++kq) {
+                const float4 k4 = kt[kq], w4 = wt[kq];
+                const float kv[4] = {k4.x * vj, k4.y * vj, k4.z * vj, k4.w * vj};
+                const float wv[4] = {w4.x, w4.y, w4.z, w4.w};
+                if (PASS != 1) {
+                    const float4 r4 = rt[kq], u4 = ut[kq];
+                    const float rv[4] = {r4.x, r4.y, r4.z, r4.w}, uv[4] = {u4.x, u4.y, u4.z, u4.w};
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) o = fmaf(rv[e], fmaf(uv[e], kv[e], s[kq * 4 + e]), o);
+                }
+#pragma unroll
+                for (int e = 0; e < 4; ++e) s[kq * 4 + e] = fmaf(wv[e], s[kq * 4 + e], kv[e]);
             }
             if (PASS != 1) part[(t * KS + run) * dim + j] = o;
         }
@@ -192,11 +202,23 @@ wkv_prefix_kernel(float* __restrict__ state, const int* __restrict__ seq_slots,
     const size_t hk = idx / dim;  // head * dim + key channel
     float* S = state + (size_t)seq_slots[seq] * per_seq + idx;
     float carry = *S;
-    for (int run = seq_first_segment[seq]; run < seq_first_segment[seq + 1]; ++run) {
-        float* at = seg_state + (size_t)run * per_seq + idx;
-        float added = *at;
-        *at = carry;
-        carry = fmaf(expf(seg_logw[(size_t)run * heads * dim + hk]), carry, added);
+    const int last = seq_first_segment[seq + 1];
+    // four runs' values are asked for together: the walk itself is a chain, its loads need not be
+    for (int run = seq_first_segment[seq]; run < last; run += 4) {
+        float added[4], decay[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const bool in = run + q < last;
+            added[q] = in ? seg_state[(size_t)(run + q) * per_seq + idx] : 0.f;
+            decay[q] = in ? seg_logw[(size_t)(run + q) * heads * dim + hk] : 0.f;
+        }
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            if (run + q < last) {
+                seg_state[(size_t)(run + q) * per_seq + idx] = carry;
+                carry = fmaf(expf(decay[q]), carry, added[q]);
+            }
+        }
     }
     *S = carry;
 }
