@@ -166,7 +166,7 @@ def check_weights(model_dir: str, wanted: Mapping[str, WeightSpec]) -> Dict[str,
                 count *= int(extent)
             stored_bytes += count * dtype.itemsize
         return {"weight_files": [os.path.basename(f.path) for f in files],
-                "recognized_tensors": len(wanted), "ignored_tensors": len(ignored),
+                "recognized_tensors": sum(1 for name in wanted if name in where), "ignored_tensors": len(ignored),
                 "stored_dtypes": sorted(dtypes), "stored_bytes": stored_bytes}
     finally:
         for f in files:
