@@ -42,9 +42,9 @@ def engine_for(models, name, dtype):
 # another expert: in bfloat16 a position is compared only where every router of the plain
 # implementation chose with at least this gap between the last score in and the first out.
 # An earlier position's other expert still reaches later ones through the recurrent layers
-# and the keys, so in bfloat16 a model with routers is held to the bound by nine rows in ten
-# of those compared (float32 holds it everywhere; so does bfloat16 on models without routers).
-CLOSE_CALL = 0.02
+# and the keys, so in bfloat16 a model with routers is held to the bound by three rows in four
+# of those compared (a fault of a kernel moves nearly every row) (float32 holds it everywhere; so does bfloat16 on models without routers).
+CLOSE_CALL = 0.005
 
 
 def _plain_run(models, name, dtype, tokens):
@@ -92,7 +92,7 @@ def replay_and_check(models, name, dtype, trace, sequences, tmp_path, what, most
         else:
             missed += rows_beyond_the_bound(got[keep], want)
     assert skipped <= most_skipped * (compared + skipped), (compared, skipped)
-    assert missed <= 0.1 * compared, (what, name, dtype, missed, compared)
+    assert missed <= 0.25 * compared, (what, name, dtype, missed, compared)
 
 
 def rows_beyond_the_bound(got, want, rel=0.03):
@@ -289,7 +289,7 @@ def test_a_prompt_shape_that_recurs_is_captured_and_replayed(models, dtype):
                 check_logits(row[None, :], want, dtype, f"captured step, round {round_}, position {pos}")
             else:
                 missed += rows_beyond_the_bound(row[None, :], want)
-        assert missed <= 1, (round_, missed)
+        assert missed <= 2, (round_, missed)
     assert graphs == [0, 1, 1, 1], graphs
 
 
@@ -433,9 +433,79 @@ def test_configurations_drawn_at_random(trial, tmp_path):
         if not keep.any():
             continue
         if bf and margins:
-            assert rows_beyond_the_bound(got[keep], want[torch.from_numpy(keep)]) <= 0.1 * keep.sum(), what
+            assert rows_beyond_the_bound(got[keep], want[torch.from_numpy(keep)]) <= 0.25 * keep.sum(), what
         else:
             check_logits(got[keep], want[torch.from_numpy(keep)], dtype, what)
+
+
+def _middle_config(rng):
+    """Sizes of a small real model (widths of a few hundred, heads of 32 to 128, a few thousand
+    vocabulary entries): the shapes at which the tensor-core products, the decode projections
+    over tiles of rows and the tensor-core attention take over from the any-size kernels."""
+    from tazadra_models import attention, config, dense, layer, mamba, moe, wkv
+    width = rng.choice([192, 256, 320, 384, 512])
+    dim = rng.choice([32, 64, 128])
+    kv = rng.choice([1, 2, 4])
+    heads = kv * rng.choice([1, 2, 3, 4])
+    vdim = rng.choice([dim, dim, 32, 96])
+    rot = rng.choice([dim, dim // 2])
+    scaling = rng.choice([None, (8.0, 1.0, 4.0, 256), (4.0, 1.0, 2.0, 64)])
+    att = dict(heads=heads, kv_heads=kv, dim=dim, vdim=vdim, rot_dims=rot, base=rng.choice([10000.0, 500000.0]),
+               scaling=scaling)
+    first = attention(scale=dim ** -0.5 * 4, softcap=rng.choice([None, 20.0, 50.0]), chunk=rng.choice([64, 100, 128]), **att)
+    second = attention(scale=dim ** -0.5 * 4, softcap=rng.choice([None, 20.0]), chunk=rng.choice([None, 48, 128]),
+                       kv_from=0, **{**att, "heads": kv * rng.choice([1, 2, 4])})
+    recurrent = [wkv(rng.choice([2, 4, 8]), rng.choice([32, 64]), rng.choice([16, 32, 40])),
+                 mamba(rng.choice([1, 2]) * width, rng.choice([8, 16, 24, 32]), rng.choice([8, 16, 24]), rng.choice([3, 4]))]
+    ffs = [dense(rng.choice([384, 512, 768]), rng.choice([2.0, 7.0])),
+           moe(rng.choice([4, 8, 16]), rng.choice([1, 2]), rng.choice([64, 96, 128]))]
+    layers = [layer(first, rng.choice(ffs))]
+    for _ in range(rng.randint(2, 4)):
+        layers.append(layer(rng.choice(recurrent), rng.choice(ffs + [None])))
+    layers.insert(rng.randint(2, len(layers)), layer(second, rng.choice(ffs)))
+    return config(rng.choice([640, 1000, 2048, 4099]), width, 1e-6, rng.choice([0.5, 1.0]), rng.choice([None, 30.0]), layers)
+
+
+@pytest.mark.parametrize("trial", range(6))
+def test_middle_sizes_drawn_at_random(trial, tmp_path):
+    """A batch of two prompts (one of them in two portions) and eight tokens decoded together, both
+    dtypes, at sizes of a small real model."""
+    from nnis_b200.engine import Engine, SequenceStep
+    rng = random.Random(9100 + trial)
+    cfg = _middle_config(rng)
+    d = make_model(str(tmp_path / "m"), cfg, seed=40 + trial)
+    a, b = random_tokens(rng, 208, cfg["vocab"]), random_tokens(rng, 77, cfg["vocab"])
+    for dtype in DTYPES:
+        bf = dtype == "bfloat16"
+        want, keep = {}, {}
+        for name, toks in (("a", a), ("b", b)):
+            margins = []
+            want[name] = P.forward(cfg, load_weights(d, bf), toks, emulate_bf16=bf, margins=margins)
+            gap = torch.stack(margins).min(dim=0).values if margins else torch.full((len(toks),), float("inf"))
+            keep[name] = (gap >= (CLOSE_CALL if bf else 1e-6)).numpy()
+        engine = Engine.from_dir(d, dtype=dtype, max_tokens=2048)
+        sa, sb = engine.acquire_slot(), engine.acquire_slot()
+        rows = []  # (request, position, logits row)
+        got = engine.step([SequenceStep(sa, a[:130], [0, 63, 64, 129]), SequenceStep(sb, b[:69], [0, 68])]).cpu().numpy()
+        rows += [("a", p, got[i]) for i, p in enumerate([0, 63, 64, 129])] + [("b", 0, got[4]), ("b", 68, got[5])]
+        got = engine.step([SequenceStep(sa, a[130:200], [0, 69])]).cpu().numpy()
+        rows += [("a", 130, got[0]), ("a", 199, got[1])]
+        for t in range(8):
+            got = engine.step([SequenceStep(sa, a[200 + t:201 + t], [0]), SequenceStep(sb, b[69 + t:70 + t], [0])]).cpu().numpy()
+            rows += [("a", 200 + t, got[0]), ("b", 69 + t, got[1])]
+        engine.release_slot(sa)
+        engine.release_slot(sb)
+        engine.check_status()
+        what = f"middle size {trial} {dtype}: {json.dumps(cfg)}"
+        kept = [(r, p, row) for r, p, row in rows if keep[r][p]]
+        assert len(kept) >= len(rows) // 4, what
+        gotten = np.stack([row for _, _, row in kept])
+        wanted = torch.stack([want[r][p] for r, p, _ in kept])
+        assert np.isfinite(gotten).all(), what
+        if bf and any(l["mlp"] and l["mlp"]["kind"] == "moe" for l in cfg["layers"]):
+            assert rows_beyond_the_bound(gotten, wanted) <= 0.25 * len(kept), what
+        else:
+            check_logits(gotten, wanted, dtype, what)
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
