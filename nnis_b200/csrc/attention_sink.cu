@@ -16,6 +16,9 @@
 //                   no value; the output is multiplied by gate[token, head].  The key range may be
 //                   cut into slices whose partial records a second kernel merges in order (the sink
 //                   counts in the first slice).
+//   attn_sink_group the same where 2, 3, 4, 6 or 8 query heads share a key/value head: one warp per
+//                   (query token, key/value head) holds all its query heads, so a key's and a value's
+//                   row is fetched once for the group instead of once a head.
 //
 // Serves prompts and single tokens, float32 and bfloat16 storage.  A row whose position is -1
 // (padding) is skipped.
@@ -211,6 +214,150 @@ attn_sink_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, const T
     }
 }
 
+// G query heads of one key/value head in one warp.  q_smem: [4 warps][G][dk] floats.
+template <typename T, int R, int G>
+__global__ void __launch_bounds__(128)
+attn_sink_group_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, const T* __restrict__ v_cache,
+                       const int* __restrict__ token_pos, const int* __restrict__ token_seq,
+                       const int* __restrict__ page_table, int table_cols, const float* __restrict__ sink,
+                       const float* __restrict__ gate, T* __restrict__ out, float* __restrict__ partial,
+                       int n_tokens, int nq, int nkv, int dk, int dv, int page_size, int window, int chunk,
+                       float scale, float cap, int n_splits) {
+    extern __shared__ __align__(16) float q_smem[];
+    pdl_wait();
+    pdl_launch_dependents();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int n = blockIdx.x * 4 + warp;
+    if (n >= n_tokens) return;
+    const int hk = blockIdx.y, split = blockIdx.z;
+    const int h0 = hk * G;  // the group's first query head
+    const int pos = token_pos[n];
+    float* qs = q_smem + (size_t)warp * G * dk;
+
+    float m[G], l[G], acc[G][R];
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+        m[g] = -FLT_MAX;
+        l[g] = 0.f;
+#pragma unroll
+        for (int r = 0; r < R; ++r) acc[g][r] = 0.f;
+    }
+    if (pos < 0) {
+        if (n_splits == 1) return;
+    } else {
+        const T* qrow = q + ((size_t)n * nq + h0) * dk;  // the group's heads are neighbours
+        for (int i = lane; i < G * dk; i += 32) qs[i] = to_float(qrow[i]);
+        __syncwarp();
+        int lo = window > 0 ? max(0, pos - window + 1) : 0;
+        if (chunk > 0) lo = max(lo, (pos / chunk) * chunk);
+        const int hi = pos + 1;
+        int per = (hi - lo + n_splits - 1) / n_splits;
+        per = (per + 31) & ~31;
+        const int start = lo + split * per;
+        const int end = min(hi, start + per);
+        if (sink && split == 0) {
+#pragma unroll
+            for (int g = 0; g < G; ++g) {
+                m[g] = sink[h0 + g];
+                l[g] = 1.f;
+            }
+        }
+        const int* table = page_table + (size_t)token_seq[n] * table_cols;
+        const float inv_cap = cap > 0.f ? 1.0f / cap : 0.f;
+        const bool by_four = (dk & 3) == 0;
+        for (int c = start; c < end; c += 32) {
+            const int t = c + lane;
+            const bool valid = t < end;
+            int row_index = 0;
+            float s[G];
+#pragma unroll
+            for (int g = 0; g < G; ++g) s[g] = 0.f;
+            if (valid) {
+                int page = table[t / page_size];
+                row_index = (page * nkv + hk) * page_size + (t % page_size);
+                const T* krow = k_cache + (size_t)row_index * dk;
+                if (by_four) {
+#pragma unroll 4
+                    for (int i = 0; i < dk; i += 4) {
+                        const float4 kv = load4(krow + i);
+#pragma unroll
+                        for (int g = 0; g < G; ++g) {
+                            const float4 qv = *reinterpret_cast<const float4*>(qs + g * dk + i);
+                            s[g] = fmaf(qv.x, kv.x, s[g]);
+                            s[g] = fmaf(qv.y, kv.y, s[g]);
+                            s[g] = fmaf(qv.z, kv.z, s[g]);
+                            s[g] = fmaf(qv.w, kv.w, s[g]);
+                        }
+                    }
+                } else {
+                    for (int i = 0; i < dk; ++i) {
+                        const float kv = to_float(krow[i]);
+#pragma unroll
+                        for (int g = 0; g < G; ++g) s[g] = fmaf(qs[g * dk + i], kv, s[g]);
+                    }
+                }
+            }
+            float p[G];
+#pragma unroll
+            for (int g = 0; g < G; ++g) {
+                float sv = s[g] * scale;
+                if (cap > 0.f) sv = cap * tanhf(sv * inv_cap);
+                sv = valid ? sv : -FLT_MAX;
+                const float m_new = fmaxf(m[g], warp_max(sv));
+                p[g] = valid ? expf(sv - m_new) : 0.f;
+                const float alpha = l[g] == 0.f ? 0.f : expf(m[g] - m_new);
+                l[g] = l[g] * alpha + warp_sum(p[g]);
+                m[g] = m_new;
+#pragma unroll
+                for (int r = 0; r < R; ++r) acc[g][r] *= alpha;
+            }
+            const int count = min(32, end - c);
+#pragma unroll 2
+            for (int j = 0; j < count; ++j) {
+                const int rj = __shfl_sync(0xffffffffu, row_index, j);
+                const T* vrow = v_cache + (size_t)rj * dv;
+                float vr[R];
+#pragma unroll
+                for (int r = 0; r < R; ++r) {
+                    int i = lane + 32 * r;
+                    vr[r] = i < dv ? to_float(vrow[i]) : 0.f;
+                }
+#pragma unroll
+                for (int g = 0; g < G; ++g) {
+                    const float pj = __shfl_sync(0xffffffffu, p[g], j);
+#pragma unroll
+                    for (int r = 0; r < R; ++r) acc[g][r] = fmaf(pj, vr[r], acc[g][r]);
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+        const int hq = h0 + g;
+        if (n_splits == 1) {
+            float inv = l[g] > 0.f ? 1.0f / l[g] : 0.f;
+            if (gate) inv *= gate[(size_t)n * nq + hq];
+            T* o = out + ((size_t)n * nq + hq) * dv;
+#pragma unroll
+            for (int r = 0; r < R; ++r) {
+                int i = lane + 32 * r;
+                if (i < dv) o[i] = from_float<T>(acc[g][r] * inv);
+            }
+        } else {
+            float* rec = partial + (((size_t)n * nq + hq) * n_splits + split) * (size_t)(dv + 2);
+            if (lane == 0) {
+                rec[0] = m[g];
+                rec[1] = l[g];
+            }
+#pragma unroll
+            for (int r = 0; r < R; ++r) {
+                int i = lane + 32 * r;
+                if (i < dv) rec[2 + i] = acc[g][r];
+            }
+        }
+    }
+}
+
 // The slices of a (token, head) added up in ascending order, times the head's gate.
 template <typename T>
 __global__ void __launch_bounds__(128)
@@ -262,9 +409,38 @@ static int launch_attn_sink(const void* q, const void* k_cache, const void* v_ca
                             const float* gate, void* out, float* partial, int n_tokens, int nq, int nkv, int dk,
                             int dv, int page_size, int window, int chunk, float scale, float cap, int n_splits,
                             cudaStream_t stream) {
+    cudaError_t e;
+    const int group = nq / nkv;
+    const size_t group_smem = 4 * (size_t)group * dk * sizeof(float);
+    if ((group == 2 || group == 3 || group == 4 || group == 6 || group == 8) && dv <= 128 &&
+        group_smem <= 48 * 1024 && nkv <= 65535) {
+        dim3 ggrid((n_tokens + 3) / 4, nkv, n_splits);
+#define NNIS_GROUP_CASE(R, G) \
+    e = launch_dependent(attn_sink_group_kernel<T, R, G>, ggrid, 128, group_smem, stream, (const T*)q, \
+                         (const T*)k_cache, (const T*)v_cache, token_pos, token_seq, page_table, table_cols, sink, \
+                         gate, (T*)out, partial, n_tokens, nq, nkv, dk, dv, page_size, window, chunk, scale, cap, \
+                         n_splits)
+#define NNIS_GROUP_R(G) \
+    if (dv <= 32) NNIS_GROUP_CASE(1, G); \
+    else if (dv <= 64) NNIS_GROUP_CASE(2, G); \
+    else NNIS_GROUP_CASE(4, G)
+        if (group == 2) { NNIS_GROUP_R(2); }
+        else if (group == 3) { NNIS_GROUP_R(3); }
+        else if (group == 4) { NNIS_GROUP_R(4); }
+        else if (group == 6) { NNIS_GROUP_R(6); }
+        else { NNIS_GROUP_R(8); }
+#undef NNIS_GROUP_R
+#undef NNIS_GROUP_CASE
+        if (e != cudaSuccess) return (int)e;
+        if (n_splits > 1) {
+            size_t rows = (size_t)n_tokens * nq;
+            e = launch_dependent(attn_sink_merge_kernel<T>, (unsigned)rows, 128, 0, stream, (const float*)partial,
+                                 gate, (T*)out, dv, n_splits);
+        }
+        return e == cudaSuccess ? NNIS_OK : (int)e;
+    }
     dim3 grid((n_tokens + 3) / 4, nq, n_splits);
     size_t smem = 4 * (size_t)dk * sizeof(float);
-    cudaError_t e;
 #define NNIS_SINK_CASE(R) \
     e = launch_dependent(attn_sink_kernel<T, R>, grid, 128, smem, stream, (const T*)q, (const T*)k_cache, \
                          (const T*)v_cache, token_pos, token_seq, page_table, table_cols, sink, gate, (T*)out, \

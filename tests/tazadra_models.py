@@ -80,7 +80,9 @@ ODD = config(211, 76, 1e-6, 1.0, None, [
 ])
 # one mechanism each
 ONLY_ATTENTION = config(150, 64, 1e-5, 0.5, None, [
-    layer(attention(4, 2, 16, 24, 8, 0.5, base=100.0, softcap=10.0, chunk=50), None)])
+    layer(attention(4, 2, 16, 24, 8, 0.5, base=100.0, softcap=10.0, chunk=50), None),
+    layer(attention(8, 1, 12, 40, 12, 0.6, base=30.0, chunk=33), None),        # eight query heads on one key/value head
+    layer(attention(5, 1, 12, 40, 12, 0.6, base=30.0, softcap=6.0, kv_from=1), None)])  # five: no kernel of the group's own
 ONLY_WKV = config(150, 64, 1e-5, 0.5, None, [layer(wkv(2, 32, 16), None)])
 WIDE_WKV = config(150, 64, 1e-5, 0.8, None, [layer(wkv(2, 72, 10), None), layer(wkv(1, 136, 4), None),
                                              layer(wkv(1, 256, 3), None)])
