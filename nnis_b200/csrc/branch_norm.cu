@@ -39,8 +39,16 @@ norm_scale_add_kernel(float* __restrict__ branch, const float* __restrict__ w,
     pdl_launch_dependents();
     const size_t row = blockIdx.x;
     float* b = branch + row * width;
+    const bool by_four = (width & 3) == 0;  // rows start on 16-byte borders: four values a load
     float ss = 0.f;
-    for (int i = threadIdx.x; i < width; i += 256) ss = fmaf(b[i], b[i], ss);
+    if (by_four) {
+        for (int i = threadIdx.x * 4; i < width; i += 1024) {
+            const float4 v = load4(b + i);
+            ss = fmaf(v.x, v.x, fmaf(v.y, v.y, fmaf(v.z, v.z, fmaf(v.w, v.w, ss))));
+        }
+    } else {
+        for (int i = threadIdx.x; i < width; i += 256) ss = fmaf(b[i], b[i], ss);
+    }
     ss = warp_sum(ss);
     if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
     __syncthreads();
@@ -49,6 +57,17 @@ norm_scale_add_kernel(float* __restrict__ branch, const float* __restrict__ w,
     for (int k = 0; k < 8; ++k) total += red[k];
     const float s = mult / sqrtf(total / (float)width + eps);
     float* h = hidden + row * width;
+    if (by_four) {
+        for (int i = threadIdx.x * 4; i < width; i += 1024) {
+            const float4 bv = load4(b + i), wv = load4(w + i), hv = load4(h + i);
+            const float4 v = make_float4(fmaf(bv.x * s, wv.x, hv.x), fmaf(bv.y * s, wv.y, hv.y),
+                                         fmaf(bv.z * s, wv.z, hv.z), fmaf(bv.w * s, wv.w, hv.w));
+            store4(h + i, v);
+            if (out) store4(out + row * width + i, v);
+            if (clear) store4(b + i, make_float4(0.f, 0.f, 0.f, 0.f));
+        }
+        return;
+    }
     for (int i = threadIdx.x; i < width; i += 256) {
         float v = fmaf(b[i] * s, w[i], h[i]);
         h[i] = v;

@@ -41,6 +41,25 @@ conv_silu_kernel(const T* __restrict__ xz, const float* __restrict__ conv_w, con
     const int first = seq_first_row ? seq_first_row[seq] : n;
     const int L = taps - 1;
     const float* tail = conv_state + (size_t)slot * L * inner;
+    if ((inner & 3) == 0) {  // four channels a thread: rows of xz and xc start on 8- or 16-byte borders
+        for (int c = (blockIdx.y * 256 + threadIdx.x) * 4; c < inner; c += 1024 * gridDim.y) {
+            float acc[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) acc[e] = conv_b ? conv_b[c + e] : 0.f;
+            for (int j = 0; j < taps; ++j) {
+                const int back = L - j;  // tokens before this one
+                const float4 in = n - back >= first ? load4(xz + (size_t)(n - back) * 2 * inner + c)
+                                                    : load4(tail + (size_t)(L - (back - (n - first))) * inner + c);
+                acc[0] = fmaf(conv_w[(size_t)c * taps + j], in.x, acc[0]);
+                acc[1] = fmaf(conv_w[(size_t)(c + 1) * taps + j], in.y, acc[1]);
+                acc[2] = fmaf(conv_w[(size_t)(c + 2) * taps + j], in.z, acc[2]);
+                acc[3] = fmaf(conv_w[(size_t)(c + 3) * taps + j], in.w, acc[3]);
+            }
+            store4(xc + (size_t)n * inner + c, make_float4(acc[0] / (1.0f + expf(-acc[0])), acc[1] / (1.0f + expf(-acc[1])),
+                                                           acc[2] / (1.0f + expf(-acc[2])), acc[3] / (1.0f + expf(-acc[3]))));
+        }
+        return;
+    }
     for (int c = blockIdx.y * 256 + threadIdx.x; c < inner; c += 256 * gridDim.y) {
         float acc = conv_b ? conv_b[c] : 0.f;
         for (int j = 0; j < taps; ++j) {
@@ -258,7 +277,7 @@ NNIS_API int nnis_conv_silu(const void* xz, const float* conv_w, const float* co
                             const int* seq_first_row, void* xc, int n_tokens, int inner, int taps, int dtype,
                             cudaStream_t stream) {
     if (n_tokens <= 0 || inner <= 0 || taps <= 0 || !xz || !conv_w || !conv_state || !xc) return NNIS_ERR_ARGUMENT;
-    dim3 grid(n_tokens, (unsigned)min(64, (inner + 255) / 256));
+    dim3 grid(n_tokens, (unsigned)min(64, ((inner & 3) ? inner + 255 : inner / 4 + 255) / 256));
     cudaError_t e;
     if (dtype == NNIS_DTYPE_F32)
         e = launch_dependent(conv_silu_kernel<float>, grid, 256, 0, stream, (const float*)xz, conv_w, conv_b,
