@@ -81,7 +81,7 @@ wkv_mix_kernel(const T* __restrict__ x, const float* __restrict__ mu, const floa
 //         the state BEFORE each run and leaves the slot's state as it is after the step;
 // PASS 2: from seg_state[run], outputs written.
 template <typename T, int KL, int PASS>
-__global__ void __launch_bounds__(1024)
+__global__ void __launch_bounds__(1024, 1)
 wkv_scan_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __restrict__ v,
                 const float* __restrict__ d, const float* __restrict__ u, float* __restrict__ state,
                 const int* __restrict__ token_pos, const int* __restrict__ token_seq,
